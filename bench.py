@@ -1,0 +1,384 @@
+"""Decode benchmark: Llama-3.2-1B architecture, bf16, batch 1, greedy.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One *step* is one request of the headline workload: a 16-token context already
+in the KV cache and 100 greedy decode tokens at positions 16..115 (seeded
+synthetic weights N(0, 0.02), synthetic prompt/KV).  The JSON line reports
+
+* ``value``      tokens/s with everything resident on the device: 100 launches of
+                 the megakernel per request, token fed back on the device;
+* ``e2e``        the same metric through ``Generator.generate`` with host
+                 buffers: the first token comes from pinned host memory and the
+                 100 produced tokens are read back, every request;
+* ``roofline``   algorithmic bytes per launch (linear weights + KV read + KV
+                 written) over the mean launch duration, against the measured
+                 HBM copy bandwidth;
+* ``cpu_baseline`` the CPU oracle (a port of the reference's PyTorch
+                 interpreter) timed on this box's cores over a few tokens.
+
+``--impl reference`` times only that CPU interpreter (one token per step).
+With N > 1 (under torchrun) every rank decodes an independent replica.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+PROMPT_LEN = 16
+TOKENS_PER_REQUEST = 100
+FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+
+MODEL = dict(hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+             intermediate_size=8192, vocab_size=128256)
+
+
+def linear_weight_bytes(cfg: dict) -> int:
+    h, inter, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * d
+    per_layer = (qkv + h + 2 * inter) * h + h * inter
+    return 2 * (cfg["num_hidden_layers"] * per_layer + cfg["vocab_size"] * h)
+
+
+def kv_bytes_per_position(cfg: dict) -> int:
+    return 2 * 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"]
+
+
+def algorithmic_bytes_per_request(cfg: dict) -> int:
+    """Sum over the 100 launches of: every linear weight once, the cached K/V of
+    positions 0..pos, and the appended K/V row."""
+    kv = kv_bytes_per_position(cfg)
+    total = 0
+    for pos in range(PROMPT_LEN, PROMPT_LEN + TOKENS_PER_REQUEST):
+        total += linear_weight_bytes(cfg) + kv * (pos + 1) + kv
+    return total
+
+
+def measured_hbm_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, sm_max, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [x for x in sm if x > 0]
+        return {"sm_mhz": statistics.median(busy or sm), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
+        dist.init_process_group(backend=backend)
+    return rank, world, local
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device="cuda" if torch.cuda.is_available() else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def build_gpu_model(device):
+    from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+    from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+    extra = ExtraModelConfig(interleave_rope=True, max_len_override=PROMPT_LEN + TOKENS_PER_REQUEST + 12)
+    model = LlamaForCausalLM.random_init(LlamaConfig(**MODEL), extra, seed=0, device=device, generate_on=device)
+    gen = torch.Generator(device=device).manual_seed(3)
+    for cache in model.stacked_kv_cache:
+        cache[:, :, :PROMPT_LEN] = torch.randn(cache[:, :, :PROMPT_LEN].shape, generator=gen, device=device).bfloat16()
+    sched = LatencyScheduleBuilder.build(model)
+    tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+    return model, sched
+
+
+def time_cpu_oracle(model_gpu, tokens: int, threads: int, warm: int = 1):
+    """Seconds per token of the CPU interpreter on a copy of the GPU model's weights."""
+    from oracle import pyvm
+    from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+
+    torch.set_num_threads(threads)
+    extra = ExtraModelConfig(interleave_rope=True, max_len_override=PROMPT_LEN + TOKENS_PER_REQUEST + 12)
+    if model_gpu is not None:
+        # same weights as the GPU arm: clone its finalised tensors to the host
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(torch.bfloat16)
+        try:
+            with torch.device("meta"):
+                cpu = LlamaForCausalLM(LlamaConfig(**MODEL), extra)
+        finally:
+            torch.set_default_dtype(prev)
+        cpu.device, cpu.dtype = torch.device("cpu"), torch.bfloat16
+        sd = {k: v.detach().to("cpu") for k, v in model_gpu.state_dict().items()}
+        cpu.load_state_dict(sd, strict=False, assign=True)
+        if MODEL.get("tie_word_embeddings", True):
+            cpu.lm_head.lm_head.weight = cpu.model.embed_tokens.embed_tokens.weight
+        cpu.model.rope_cos = model_gpu.model.rope_cos.cpu()
+        cpu.model.rope_sin = model_gpu.model.rope_sin.cpu()
+        cpu.requires_grad_(False)
+        cpu.stack_params()
+        cpu.setup_caches()
+        for dst, src in zip(cpu.stacked_kv_cache, model_gpu.stacked_kv_cache):
+            dst.copy_(src.cpu())
+    else:
+        cpu = LlamaForCausalLM.random_init(LlamaConfig(**MODEL), extra, seed=0, device="cpu")
+    sched = LatencyScheduleBuilder.build(cpu)
+    instr = sched.get_linear_instructions()
+    tok = torch.tensor([[17]])
+    times = []
+    for i in range(warm + tokens):
+        t0 = time.perf_counter()
+        tok = pyvm.pyvm_step(cpu, sched, instr, tok.view(1, 1), PROMPT_LEN + i).view(1, 1)
+        if i >= warm:
+            times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU path for this workload: its PyTorch interpreter of the
+    instruction stream (restated under oracle/), all host threads, one decode
+    token per step."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    model_gpu = None
+    if torch.cuda.is_available():
+        model_gpu, _ = build_gpu_model("cuda:0")
+    times = time_cpu_oracle(model_gpu, args.steps, threads, warm=args.warmup)
+    total = sum(times)
+    tps = len(times) / total
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "llama-3.2-1b-arch bf16 batch-1 greedy decode, 16-token context, positions 16..",
+                   "step": "one decode token on the host cores (bounded sample of the 100-token request)"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{len(times)} decode tokens of the 16-layer model, PyTorch interpreter, {threads} threads"},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local):
+    from thor_megakernels_b200.generators import MK_FusedGenerator
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py measures the CUDA megakernel; no CUDA device is visible")
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    model, sched = build_gpu_model(device)
+    gen = MK_FusedGenerator(model, sched)
+    mk = gen.mk
+    stream = torch.cuda.current_stream(device)
+    first = torch.tensor([17], dtype=torch.int32, device=device)
+    produced = torch.zeros(TOKENS_PER_REQUEST, dtype=torch.int32, device=device)
+
+    def request_resident():
+        mk.decode(first, produced, start_pos=PROMPT_LEN, count=TOKENS_PER_REQUEST, stream=stream)
+
+    for _ in range(max(args.warmup, 3)):
+        request_resident()
+    torch.cuda.synchronize(device)
+    mk.status()
+
+    sampler = ClockSampler(local)
+    barrier(world)
+    torch.cuda.synchronize(device)
+    sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(args.steps):
+        request_resident()
+    end.record(stream)
+    torch.cuda.synchronize(device)
+    barrier(world)
+    clocks = sampler.stop()
+    mk.status()
+    elapsed_ms = max_over_ranks(start.elapsed_time(end), world)
+    launches = args.steps * TOKENS_PER_REQUEST
+    ms_per_step = elapsed_ms / args.steps
+    tokens_per_s = world * launches / (elapsed_ms / 1000.0)
+
+    # ---- end to end through Generator.generate with host buffers ----
+    host_in = torch.tensor([[17] + [0] * TOKENS_PER_REQUEST], dtype=torch.long).pin_memory()
+    host_out = torch.zeros((1, TOKENS_PER_REQUEST + 1), dtype=torch.long).pin_memory()
+    dev_tokens = torch.zeros((1, TOKENS_PER_REQUEST + 1), dtype=torch.long, device=device)
+
+    def request_e2e():
+        dev_tokens[:, :1].copy_(host_in[:, :1], non_blocking=True)
+        gen.generate(dev_tokens, prompt_len=PROMPT_LEN, ntok=TOKENS_PER_REQUEST, ntok_already_generated=1)
+        host_out[:, 1:].copy_(dev_tokens[:, 1:], non_blocking=True)
+        stream.synchronize()
+
+    for _ in range(3):
+        request_e2e()
+    barrier(world)
+    torch.cuda.synchronize(device)
+    start.record(stream)
+    for _ in range(args.steps):
+        request_e2e()
+    end.record(stream)
+    torch.cuda.synchronize(device)
+    e2e_ms = max_over_ranks(start.elapsed_time(end), world)
+    e2e_tps = world * launches / (e2e_ms / 1000.0)
+    assert torch.equal(host_out[0, 1:].to(torch.int32), produced.cpu()), "e2e and resident loops disagree"
+
+    line = None
+    if rank == 0:
+        peak, peak_src = measured_hbm_peak()
+        bytes_per_launch = algorithmic_bytes_per_request(MODEL) / TOKENS_PER_REQUEST
+        launch_ms = elapsed_ms / launches
+        achieved = bytes_per_launch / (launch_ms / 1000.0) / 1e9
+        line = {
+            "metric": "decode_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": ("SELF-TEST (2 layers, small vocabulary) - not the benchmark workload" if args.self_test else
+                             "llama-3.2-1b-arch bf16 batch-1 greedy decode: 16-token context, 100 tokens (pos 16..115)"),
+                "step": "one 100-token request = 100 megakernel launches",
+                "ms_per_token": launch_ms,
+                "l2": "inputs larger than L2 (2.47 GB of weights streamed per launch vs 126 MB)",
+                "parallelism": "replicas" if world > 1 else "single",
+                "schedule": "reference latency schedule, round-robin, 148 queues",
+            },
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": MEASURED_DRAM_TRAFFIC_PER_LAUNCH, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": bytes_per_launch, "launch_ms": launch_ms,
+                         "frac_of_nominal_8TBs": achieved / 8000.0},
+            "e2e": {"value": e2e_tps, "unit": "tokens/s", "h2d_bytes_per_step": 8,
+                    "d2h_bytes_per_step": 8 * TOKENS_PER_REQUEST, "api": "MK_FusedGenerator.generate",
+                    "ms_per_token": e2e_ms / launches},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+    # CPU baseline: rank 0, single-GPU runs only
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        times = time_cpu_oracle(model, args.cpu_tokens, threads)
+        line["cpu_baseline"] = {"value": len(times) / sum(times), "unit": "tokens/s", "cores": threads, "kind": "port",
+                                "sample": f"{len(times)} decode tokens of the same 16-layer model through the CPU "
+                                          f"interpreter (oracle/pyvm.py), {threads} threads"}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one megakernel launch from an ncu capture
+# (profiles/); None until a capture of this workload exists.
+MEASURED_DRAM_TRAFFIC_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-tokens", type=int, default=4, help="decode tokens timed for cpu_baseline")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--self-test", action="store_true",
+                    help="2-layer, 4096-token-vocabulary model to exercise this script quickly; not a benchmark")
+    args = ap.parse_args()
+    if args.self_test:
+        MODEL.update(num_hidden_layers=2, vocab_size=4096)
+    rank, world, local = dist_setup(args.gpus)
+    try:
+        if args.impl == "reference":
+            run_reference(args, rank, world)
+        else:
+            run_ours(args, rank, world, local)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

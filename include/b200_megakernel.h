@@ -1,0 +1,226 @@
+/*
+ * C ABI of the B200 decode megakernel library (libb200mk.so).
+ *
+ * Everything a host needs to drive one Llama decode step on an sm_100a GPU:
+ * plain pointers and sizes, int return codes (0 = success, otherwise a
+ * cudaError_t value or one of the MK_ERR_* codes below), no exceptions and no
+ * framework types.  All pointers named "device" are CUDA device pointers owned
+ * by the caller; the library borrows them for the lifetime of the handle.
+ *
+ * Each entry point names the interface of the reference project
+ * (yiannisha/thor-megakernels) that it stands in for.
+ */
+#ifndef B200_MEGAKERNEL_H
+#define B200_MEGAKERNEL_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MK_ABI_VERSION 1
+
+/* error codes beyond cudaError_t (which stay below 10000) */
+#define MK_ERR_BAD_ARGUMENT 10001  /* null pointer, negative size, ABI version mismatch */
+#define MK_ERR_UNSUPPORTED  10002  /* shape the kernel is not built for              */
+#define MK_ERR_RESIDENCY    10003  /* grid cannot be co-resident / smem over budget  */
+#define MK_ERR_DEVICE_WAIT  10004  /* a bounded device-side wait ran out; see mk_status */
+
+/* mk_step flags */
+#define MK_STEP_EMBED          1u  /* layer-0 input is embed_w[*token_in] instead of hidden_states */
+#define MK_STEP_RESET_BARRIERS 2u  /* the kernel zeroes `barriers` when it finishes               */
+#define MK_STEP_WRITE_TOKEN    4u  /* greedy token (argmax of logits) is written to *token_out     */
+#define MK_STEP_TIMINGS        8u  /* per-instruction clock stamps are written to `timings`        */
+
+/* weight formats */
+#define MK_WEIGHTS_BF16  0
+#define MK_WEIGHTS_NVFP4 1
+
+/*
+ * One NVFP4 weight matrix [rows, k]: E2M1 codes two per byte (element 2j in the
+ * low nibble), one E4M3 scale byte per 16 consecutive k, one fp32 tensor scale.
+ * Layout of the reference quantiser, tools/analysis/nvfp4/primitive.cu:50-75
+ * ("packed" and "canonical" outputs).
+ */
+typedef struct MkNvfp4Matrix {
+    const uint8_t *packed;   /* device, [rows, k/2]  */
+    const uint8_t *scales;   /* device, [rows, k/16] */
+    float tensor_scale;
+} MkNvfp4Matrix;
+
+/*
+ * Model and buffer table.  Field meaning and dtypes are those of the
+ * reference's kernel globals (demos/low-latency-llama/llama.cuh:82-147) and of
+ * the 27 positional arguments of its native call
+ * (megakernels/demos/latency/mk.py:15-48); shapes are runtime values here.
+ */
+typedef struct MkModelDesc {
+    int32_t abi_version;           /* MK_ABI_VERSION */
+    int32_t weight_format;         /* MK_WEIGHTS_* */
+
+    int32_t hidden_size;
+    int32_t num_layers;
+    int32_t num_q_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim;
+    int32_t intermediate_size;
+    int32_t vocab_size;
+    float   attn_scale;
+    float   rms_norm_eps;
+
+    /* bf16 weights, layer-major stacks (MK_WEIGHTS_BF16) */
+    const void *qkv_w;             /* [L, (Hq+2Hkv)*D, hidden] */
+    const void *o_w;               /* [L, hidden, Hq*D]        */
+    const void *up_w;              /* [L, inter, hidden]       */
+    const void *gate_w;            /* [L, inter, hidden]       */
+    const void *down_w;            /* [L, hidden, inter]       */
+    const void *lm_head_w;         /* [vocab, hidden]          */
+    /* norm weights are bf16 in both formats */
+    const void *attn_norm_w;       /* [L, hidden] */
+    const void *mlp_norm_w;        /* [L, hidden] */
+    const void *lm_head_norm_w;    /* [hidden]    */
+    const void *embed_w;           /* [vocab, hidden] bf16, may be NULL (then MK_STEP_EMBED is refused) */
+
+    /* NVFP4 weights (MK_WEIGHTS_NVFP4): arrays of num_layers entries, except lm_head */
+    const MkNvfp4Matrix *qkv_q;
+    const MkNvfp4Matrix *o_q;
+    const MkNvfp4Matrix *up_q;
+    const MkNvfp4Matrix *gate_q;
+    const MkNvfp4Matrix *down_q;
+    const MkNvfp4Matrix *lm_head_q; /* one entry */
+
+    /* KV cache [L, kv_batch, kv_max_len, Hkv, D] bf16 (kv_batch sequences, only index 0 is decoded) */
+    void   *k_cache;
+    void   *v_cache;
+    int32_t kv_batch;
+    int32_t kv_max_len;
+
+    /* rotary tables fp32 [rope_positions, D], adjacent-pair ("interleaved") column order */
+    const float *rope_cos;
+    const float *rope_sin;
+    int32_t rope_positions;
+
+    /* activation buffers */
+    void  *hidden_states;          /* bf16 [hidden]: step input (unless MK_STEP_EMBED) and step output */
+    void  *q_post_rope;            /* bf16 [Hq*D] */
+    void  *attn_out;               /* bf16 [Hq*D] */
+    float *attn_lse_intermediates; /* fp32 [Hq, max_partials]    */
+    float *attn_out_intermediates; /* fp32 [Hq, max_partials, D] */
+    int32_t max_partials;
+    void  *silu_out;               /* bf16 [inter] */
+    void  *logits;                 /* bf16 [vocab] */
+
+    /* dependency counters int32 [L, barrier_rows, barrier_cols]; zero before every step */
+    int32_t *barriers;
+    int32_t barrier_rows;          /* >= 8 */
+    int32_t barrier_cols;          /* >= Hq + 2*Hkv */
+    int32_t skip_attn_reduction;   /* 1: attention writes attn_out directly (single slice per KV head) */
+} MkModelDesc;
+
+/* Launch facts, the fields of the dict the reference's binding returns
+ * (include/checked_binding.cuh:68-95) that have a meaning here. */
+typedef struct MkLaunchInfo {
+    int32_t cooperative_launch;
+    int32_t physical_sms;
+    int32_t resident_worker_capacity;
+    int32_t active_workers;
+    int32_t threads_per_cta;
+    int32_t consumer_warps;
+    int32_t registers_per_thread;
+    int32_t local_bytes_per_thread;
+    int32_t static_smem_bytes;
+    int32_t dynamic_smem_bytes;
+    int32_t stage_count;           /* weight ring depth ("page_count")  */
+    int32_t stage_bytes;           /* bytes per ring stage ("page_size") */
+    int32_t resident_ctas_per_sm;
+    int32_t queue_len;
+    int64_t scratch_bytes;         /* device memory the handle allocated itself */
+} MkLaunchInfo;
+
+/* Status words of the last step, written by the device when a bounded wait
+ * gives up.  code 0 = clean. */
+typedef struct MkStatus {
+    int32_t code;      /* 0 ok, 1 dependency counter wait, 2 weight-ring wait, 3 partial-buffer wait, 4 unknown opcode */
+    int32_t worker;    /* CTA index */
+    int32_t opcode;
+    int32_t slot;      /* position in that worker's queue */
+    int32_t detail;    /* counter value seen / stage index */
+    int32_t expected;
+} MkStatus;
+
+/* sizeof() of the structs above as this library was compiled (0 MkModelDesc,
+ * 1 MkLaunchInfo, 2 MkStatus, 3 MkNvfp4Matrix); lets a foreign-language binding
+ * verify its own struct layout.  No counterpart in the reference. */
+int mk_abi_sizeof(int32_t which);
+
+/* Thread-local description of the last failure (reference: nv_error(),
+ * tools/analysis/nvfp4/primitive.cu:98-99). */
+const char *mk_last_error(void);
+
+/*
+ * Bind a model once.  Replaces the per-call marshalling of 27 tensors into
+ * kernel globals that the reference's binding repeats on every step
+ * (include/checked_binding.cuh:17-21).  Checks shapes, shared-memory budget and
+ * co-residency before anything is launched (checked_binding.cuh:29-67) and
+ * allocates the handle's own scratch (split-K partial sums, status words,
+ * argmax cell) with cudaMalloc on the current device.
+ */
+int mk_create(const MkModelDesc *desc, void **handle);
+
+/*
+ * Attach the instruction and timing queues: int32 [workers, queue_len, 32] and
+ * int32 [workers, queue_len, 128] device tensors as produced by
+ * tensorize_instructions (megakernels/scheduler.py:380-413).  workers must not
+ * exceed the device's SM count.  May be called again to swap schedules.
+ */
+int mk_set_schedule(void *handle, const int32_t *instructions, int32_t *timings,
+                    int32_t workers, int32_t queue_len);
+
+/*
+ * Run one decode step at position pos_id on `stream` (a cudaStream_t).
+ * Stands in for mk_llama.mk_llama(...) (demos/low-latency-llama/llama.cu:24-53;
+ * call site megakernels/demos/latency/mk.py:15-49).  token_in/token_out are
+ * device int32 cells used only with MK_STEP_EMBED / MK_STEP_WRITE_TOKEN.
+ * Asynchronous; device-side wait failures surface through mk_status.
+ */
+int mk_step(void *handle, int32_t pos_id, uint32_t flags,
+            const int32_t *token_in, int32_t *token_out, void *stream);
+
+/* The reference binding's dry_run=True result (checked_binding.cuh:95). */
+int mk_query(void *handle, MkLaunchInfo *info);
+
+/* Synchronises `stream`, copies the status words back and clears them.
+ * Returns MK_ERR_DEVICE_WAIT when code != 0.  (Reference: optional
+ * MK_GMEM_TIMEOUT_CYCLES trap, include/gmem_barrier.cuh:38-47 - here the
+ * kernel returns normally and reports.) */
+int mk_status(void *handle, MkStatus *status, void *stream);
+
+/* Budget of every device-side wait in SM clock cycles (default 4e9). */
+int mk_set_wait_budget(void *handle, int64_t cycles);
+
+void mk_destroy(void *handle);
+
+/*
+ * NVFP4 quantiser: bf16 [rows, k] -> packed codes, E4M3 block scales and,
+ * optionally, the fp32 decode of what was stored.  Same arithmetic and argument
+ * order as nv_quantize (tools/analysis/nvfp4/primitive.cu:50-75, :104-111)
+ * without the tensor-core-native scale layout.  k must be a multiple of 16.
+ */
+int mk_nvfp4_quantize(const void *input_bf16, void *packed, void *scales, float *decoded,
+                      int32_t rows, int32_t k, float tensor_scale, void *stream);
+
+/*
+ * Batch-`batch` GEMV y[b, m] = W[m, k] . x[b, k] with bf16 activations and
+ * output, fp32 accumulation.  packed != 0: NVFP4 weight-only (fused
+ * dequantise), else bf16 weights in `w`.  Mirrors nv_simt
+ * (tools/analysis/nvfp4/primitive.cu:79-96, :112-119) and wo_run
+ * (experimental/weight_only_fp4/primitive.cu:78-82); batch is 1..8.
+ */
+int mk_gemv(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y,
+            int32_t m, int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_MEGAKERNEL_H */

@@ -1,0 +1,345 @@
+"""GPU parity of the bf16 decode megakernel against the golden vectors that the
+reference's own interpreter produced (tests/golden/*.npz) and against the CPU
+oracle run live on the same seeded inputs.  Everything goes through the C-ABI
+library via the ``mk_llama`` shim or the ``Megakernel`` handle.
+
+Tolerances: token ids, dependency counters and instruction tensors are exact;
+bf16 activations, cache rows, hidden states and logits must satisfy
+``|a - ref| <= 3e-2 + 1e-2 * |ref|`` per step, teacher-forced on the
+reference's token stream.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close, bf16_from_u16, build_model, build_schedule, load_golden, load_prefill, mismatch_report
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    meta, arrays = load_golden("tiny")
+    model = build_model(meta["config"], meta["max_len"], device="cuda")
+    return meta, arrays, model
+
+
+def _mk_generator(model, sched):
+    from thor_megakernels_b200.dispatch import make_mk_interpreter
+    from thor_megakernels_b200.generators import MK_Generator
+
+    return MK_Generator(model, make_mk_interpreter("latency"), sched)
+
+
+def test_tiny_every_buffer_every_step(tiny):
+    meta, arrays, model = tiny
+    sched = build_schedule(model)
+    assert torch.equal(sched.globs.instructions.cpu(), torch.from_numpy(arrays["instructions_rr"]))
+    n = load_prefill(model, arrays)
+    gen = _mk_generator(model, sched)
+    g = sched.globs
+    tokens = arrays["tokens"]
+    for step in range(meta["ntok"]):
+        pos = n + step
+        out = gen.run(torch.tensor([[int(tokens[step])]], device="cuda"), pos_id=pos)
+        torch.cuda.synchronize()
+        assert_close("hidden", g.hidden_states, bf16_from_u16(arrays["hidden"][step]))
+        assert_close("q", g.post_ln_rope_q, bf16_from_u16(arrays[f"q_step{step}"]))
+        assert_close("attn_out", g.attn_out, bf16_from_u16(arrays[f"attn_out_step{step}"]))
+        assert_close("silu_out", g.silu_out, bf16_from_u16(arrays[f"silu_out_step{step}"]))
+        assert_close("logits", g.logits, bf16_from_u16(arrays[f"logits_step{step}"]))
+        assert_close("k_row", model.stacked_kv_cache[0][:, 0, pos], bf16_from_u16(arrays[f"k_row_step{step}"]))
+        assert_close("v_row", model.stacked_kv_cache[1][:, 0, pos], bf16_from_u16(arrays[f"v_row_step{step}"]))
+        # dependency counters: rows 0..5 are the reference interpreter's protocol
+        got = g.barriers.cpu().numpy()[:, :6]
+        assert np.array_equal(got, arrays[f"barriers_step{step}"][:, :6])
+        margin = float(arrays["top2_margin"][step])
+        if int(out) != int(tokens[step + 1]):
+            assert margin <= 2 * 0.0625, f"token mismatch at step {step} with oracle margin {margin}"
+
+
+def test_tiny_matches_live_oracle_and_fused_loop(tiny):
+    """The fused loop (in-kernel embedding, counter reset, argmax) produces the
+    same tokens and buffers as the reference-protocol loop, and the CPU oracle,
+    fed the same tokens, agrees step by step."""
+    from oracle import pyvm
+    from thor_megakernels_b200.generators import MK_FusedGenerator
+
+    meta, arrays, model = tiny
+    n = load_prefill(model, arrays)
+    sched = build_schedule(model)
+    first = int(arrays["tokens"][0])
+    ntok = 6
+
+    out_a = torch.zeros((1, ntok + 1), dtype=torch.long, device="cuda")
+    out_a[0, 0] = first
+    _mk_generator(model, sched).generate(out_a, prompt_len=n, ntok=ntok)
+    hidden_a = sched.globs.hidden_states.clone()
+    logits_a = sched.globs.logits.clone()
+
+    load_prefill(model, arrays)
+    model.stacked_kv_cache[0][:, :, n:] = 0
+    model.stacked_kv_cache[1][:, :, n:] = 0
+    out_b = torch.zeros_like(out_a)
+    out_b[0, 0] = first
+    fused = MK_FusedGenerator(model, sched)
+    fused.generate(out_b, prompt_len=n, ntok=ntok)
+    torch.cuda.synchronize()
+    fused.mk.status()
+    assert out_a.tolist() == out_b.tolist()
+    assert torch.equal(hidden_a, sched.globs.hidden_states)
+    assert torch.equal(logits_a, sched.globs.logits)
+    assert int(sched.globs.barriers.abs().sum()) == 0, "fused step must leave the counters reset"
+
+    # CPU oracle, teacher-forced on the GPU's tokens
+    cpu_model = build_model(meta["config"], meta["max_len"], device="cpu")
+    cpu_sched = build_schedule(cpu_model)
+    load_prefill(cpu_model, arrays)
+    got = out_a[0].tolist()
+    for i in range(ntok):
+        nxt = pyvm.pyvm_step(cpu_model, cpu_sched, cpu_sched.get_linear_instructions(), torch.tensor([[got[i]]]), n + i)
+        if int(nxt) != got[i + 1]:
+            top2 = torch.topk(cpu_sched.globs.logits.float(), 2).values
+            assert float(top2[0] - top2[1]) <= 0.125, (i, int(nxt), got[i + 1])
+    assert_close("hidden", sched.globs.hidden_states, cpu_sched.globs.hidden_states)
+    assert_close("logits", sched.globs.logits, cpu_sched.globs.logits)
+
+
+@pytest.mark.parametrize("mode", ["zz", "wave", "dag"])
+def test_tiny_other_assignment_policies(tiny, mode):
+    """Any valid queue assignment gives bit-identical results: the arithmetic
+    does not depend on which SM runs an instruction."""
+    meta, arrays, model = tiny
+    n = load_prefill(model, arrays)
+    tok = torch.tensor([[int(arrays["tokens"][0])]], device="cuda")
+    ref_sched = build_schedule(model, "rr")
+    _mk_generator(model, ref_sched).run(tok, pos_id=n)
+    torch.cuda.synchronize()
+    want = {k: getattr(ref_sched.globs, k).clone() for k in ("hidden_states", "logits", "silu_out", "attn_out")}
+    sched = build_schedule(model, mode)
+    _mk_generator(model, sched).run(tok, pos_id=n)
+    torch.cuda.synchronize()
+    for k, v in want.items():
+        assert torch.equal(getattr(sched.globs, k), v), k
+
+
+@pytest.mark.parametrize("stop_after_op,layer_limit", [("qkv", 1), ("partial", 1), ("oproj", 1), ("upgate", 1), ("downproj", 1), (None, 1)])
+def test_tiny_truncated_schedules(tiny, stop_after_op, layer_limit):
+    """Schedules cut after an op (the reference's diff_test workflow) against the oracle."""
+    from oracle import pyvm
+
+    meta, arrays, model = tiny
+    cpu_model = build_model(meta["config"], meta["max_len"], device="cpu")
+    load_prefill(cpu_model, arrays)
+    n = load_prefill(model, arrays)
+    kwargs = dict(stop_after_op=stop_after_op, layer_limit=layer_limit)
+    cpu_sched = build_schedule(cpu_model, **kwargs)
+    sched = build_schedule(model, **kwargs)
+    gen = torch.Generator().manual_seed(5)
+    h0 = torch.randn(meta["config"]["hidden_size"], generator=gen).bfloat16()
+    for s, dev in ((cpu_sched, "cpu"), (sched, "cuda")):
+        s.globs.hidden_states[:] = h0.to(dev)
+        s.globs.barriers.zero_()
+        s.globs.pos_id = n
+    pyvm.interpret_with_pyvm(cpu_sched.globs, cpu_sched.get_linear_instructions())
+    from thor_megakernels_b200.dispatch import make_mk_interpreter
+
+    make_mk_interpreter("latency").interpret(sched.globs)
+    torch.cuda.synchronize()
+    for name in ("hidden_states", "post_ln_rope_q", "attn_out", "silu_out"):
+        assert_close(name, getattr(sched.globs, name), getattr(cpu_sched.globs, name))
+    assert torch.equal(sched.globs.barriers.cpu()[:, :6], cpu_sched.globs.barriers[:, :6])
+
+
+@pytest.mark.parametrize("partitions,context", [(2, 40), (3, 61), (8, 200), (24, 600)])
+def test_split_attention_with_reduction(partitions, context):
+    """Cache split across several CTAs plus the log-sum-exp merge, against the
+    oracle, with seeded N(0,1) keys/values and garbage beyond the context."""
+    from oracle import pyvm
+    from thor_megakernels_b200.dispatch import make_mk_interpreter
+
+    cfg = dict(hidden_size=2048, num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+               intermediate_size=8192, vocab_size=4096)
+    cpu_model = build_model(cfg, 1024, device="cpu", seed=3)
+    model = build_model(cfg, 1024, device="cuda", seed=3)
+    gen = torch.Generator().manual_seed(11)
+    for idx in range(2):
+        kv = torch.randn(cpu_model.stacked_kv_cache[idx].shape, generator=gen).bfloat16()
+        kv[:, :, context:] *= 100.0
+        cpu_model.stacked_kv_cache[idx].copy_(kv)
+        model.stacked_kv_cache[idx].copy_(kv.cuda())
+    h0 = torch.randn(2048, generator=gen).bfloat16()
+    kwargs = dict(skip_attn_reduction=False, num_attention_partitions=partitions, stop_after_op="oproj", layer_limit=1)
+    cpu_sched, sched = build_schedule(cpu_model, **kwargs), build_schedule(model, **kwargs)
+    for s, dev in ((cpu_sched, "cpu"), (sched, "cuda")):
+        s.globs.hidden_states[:] = h0.to(dev)
+        s.globs.barriers.zero_()
+        s.globs.pos_id = context
+    pyvm.interpret_with_pyvm(cpu_sched.globs, cpu_sched.get_linear_instructions())
+    make_mk_interpreter("latency").interpret(sched.globs)
+    torch.cuda.synchronize()
+    assert_close("attn_out", sched.globs.attn_out, cpu_sched.globs.attn_out)
+    assert_close("hidden_states", sched.globs.hidden_states, cpu_sched.globs.hidden_states)
+    lse_g = sched.globs.attn_lse_intermediates[:, :partitions].cpu()
+    lse_c = cpu_sched.globs.attn_lse_intermediates[:, :partitions]
+    assert torch.allclose(lse_g, lse_c, atol=1e-3, rtol=1e-4)
+    assert torch.equal(sched.globs.barriers.cpu()[:, :6], cpu_sched.globs.barriers[:, :6])
+
+
+def test_launch_facts_and_admission_errors(tiny):
+    from thor_megakernels_b200.mk import get_mk_func
+    from thor_megakernels_b200.demos.latency.mk import interpret_with_mk
+
+    meta, arrays, model = tiny
+    sched = build_schedule(model)
+    g = sched.globs
+    mk_func = get_mk_func()
+    k4, v4 = g.k_cache.flatten(0, 1), g.v_cache.flatten(0, 1)
+    args = [g.barriers, g.instructions, g.timings, g.qkv_proj_weights, g.attn_ln_weights, g.o_proj_weights,
+            g.mlp_ln_weights, g.up_proj_weights, g.gate_proj_weights, g.down_proj_weights,
+            g.lm_head_norm_weights.data, g.lm_head_weights.data, k4, v4, g.rope_cos, g.rope_sin, g.hidden_states,
+            g.post_ln_rope_q, g.attn_out, g.attn_lse_intermediates, g.attn_out_intermediates, g.silu_out, g.logits,
+            0, g.attn_scale, g.rms_norm_eps, g.skip_attn_reduction]
+    info = mk_func(*args, dry_run=True)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert info["cooperative_launch"] is True
+    assert info["physical_sms"] == sms and info["active_workers"] == g.instructions.shape[0]
+    assert info["threads_per_cta"] == 320 and info["local_bytes_per_thread"] == 0
+    assert info["dynamic_smem_bytes"] <= 227 * 1024 and info["resident_ctas_per_sm"] == 1
+    # more queues than SMs: refused before launch
+    too_many = torch.zeros((sms + 1, 1, 32), dtype=torch.int32, device="cuda")
+    bad = list(args)
+    bad[1], bad[2] = too_many, torch.zeros((sms + 1, 1, 128), dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError):
+        mk_func(*bad, dry_run=True)
+    # timing tensor that does not match the instruction tensor
+    bad = list(args)
+    bad[2] = torch.zeros((g.instructions.shape[0], 1, 128), dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError):
+        mk_func(*bad, dry_run=True)
+    # position beyond the cache
+    bad = list(args)
+    bad[23] = meta["max_len"]
+    with pytest.raises(RuntimeError):
+        mk_func(*bad)
+    # empty and all-NoOp queues are legal and do nothing
+    before = g.hidden_states.clone()
+    for depth in (0, 1, 3, 17):
+        bad = list(args)
+        bad[1] = torch.zeros((sms, depth, 32), dtype=torch.int32, device="cuda")
+        bad[2] = torch.zeros((sms, depth, 128), dtype=torch.int32, device="cuda")
+        mk_func(*bad)
+    for workers in (1, 3):
+        bad = list(args)
+        bad[1] = torch.zeros((workers, 2, 32), dtype=torch.int32, device="cuda")
+        bad[2] = torch.zeros((workers, 2, 128), dtype=torch.int32, device="cuda")
+        mk_func(*bad)
+    torch.cuda.synchronize()
+    assert torch.equal(before, g.hidden_states)
+
+
+def test_bounded_wait_reports_status_instead_of_hanging(tiny):
+    """A dependency counter that nothing ever raises: the wait runs out, the
+    kernel returns, the status words say which worker/opcode/slot gave up, and
+    the handle keeps working afterwards."""
+    from thor_megakernels_b200.demos.latency.instructions import O_ProjResidual
+    from thor_megakernels_b200.runtime import Megakernel, MegakernelError
+    from thor_megakernels_b200.scheduler import tensorize_instructions
+    from types import SimpleNamespace
+
+    meta, arrays, model = tiny
+    sched = build_schedule(model)
+    g = sched.globs
+    mk = Megakernel.from_globals(g)
+    holder = SimpleNamespace(sm_count=lambda: 2, device="cuda")
+    tensorize_instructions(holder, [[O_ProjResidual(0, 0, 1, 0)], []])  # waits for attention that never runs
+    mk.set_schedule(holder.instructions, holder.timings)
+    mk.set_wait_budget(2_000_000)  # about a millisecond
+    g.barriers.zero_()
+    mk.step(0)
+    with pytest.raises(MegakernelError) as err:
+        mk.status()
+    st = err.value.status
+    assert (st["code"], st["worker"], st["opcode"], st["slot"], st["detail"], st["expected"]) == (1, 0, 4, 0, 0, 32)
+    # the same handle runs a full step afterwards
+    mk.set_wait_budget(4_000_000_000)
+    mk.set_schedule(g.instructions, g.timings)
+    n = load_prefill(model, arrays)
+    emb = model.model.embed_tokens.embed_tokens.weight
+    g.hidden_states[:] = emb[int(arrays["tokens"][0])]
+    g.barriers.zero_()
+    mk.step(n)
+    assert mk.status()["code"] == 0
+    assert_close("hidden", g.hidden_states, bf16_from_u16(arrays["hidden"][0]))
+
+
+def test_timing_slots_are_filled(tiny):
+    from thor_megakernels_b200.runtime import MK_STEP_TIMINGS, Megakernel
+
+    meta, arrays, model = tiny
+    sched = build_schedule(model)
+    g = sched.globs
+    n = load_prefill(model, arrays)
+    mk = Megakernel.from_globals(g)
+    g.hidden_states[:] = model.model.embed_tokens.embed_tokens.weight[int(arrays["tokens"][0])]
+    g.barriers.zero_()
+    mk.step(n, flags=MK_STEP_TIMINGS)
+    mk.status()
+    t = g.timings.cpu()
+    ops = g.instructions.cpu()[:, :, 0]
+    started, ended = t[:, :, 11], t[:, :, 52]
+    assert bool(((ended > started) | (ops == 0)).all())
+    assert int(t[ops == 0].abs().sum()) == 0
+
+
+@pytest.fixture(scope="module")
+def llama1b():
+    meta, arrays = load_golden("llama1b")
+    model = build_model(meta["config"], meta["max_len"], device="cuda")
+    return meta, arrays, model
+
+
+def test_llama1b_weights_match_the_fixture(llama1b):
+    import hashlib
+
+    meta, arrays, model = llama1b
+    got = hashlib.sha256(model.stacked_params.down_proj.cpu().view(torch.int16).numpy().tobytes()).hexdigest()
+    assert got == meta["weights_sha256"]["down_proj"]
+
+
+def test_llama1b_100_tokens_teacher_forced(llama1b):
+    """Llama-3.2-1B architecture, 16-token prompt, 100 decode steps: every
+    step's hidden state, logits (top-8, 256 fixed samples, three full vectors)
+    and appended cache rows against the reference interpreter's run."""
+    meta, arrays, model = llama1b
+    sched = build_schedule(model)
+    n = load_prefill(model, arrays)
+    gen = _mk_generator(model, sched)
+    g = sched.globs
+    tokens = arrays["tokens"]
+    sample_idx = torch.from_numpy(arrays["logit_sample_idx"]).long().cuda()
+    mismatches, worst_hidden, worst_logit, exact = [], 0.0, 0.0, []
+    for step in range(meta["ntok"]):
+        pos = n + step
+        out = gen.run(torch.tensor([[int(tokens[step])]], device="cuda"), pos_id=pos)
+        rep = assert_close(f"hidden[{step}]", g.hidden_states, bf16_from_u16(arrays["hidden"][step]))
+        worst_hidden = max(worst_hidden, rep["max_abs"])
+        exact.append(rep["exact_fraction"])
+        rep = assert_close(f"logit samples[{step}]", g.logits[sample_idx], bf16_from_u16(arrays["logit_sample_val"][step]))
+        worst_logit = max(worst_logit, rep["max_abs"])
+        top = torch.from_numpy(arrays["top8_idx"][step]).long().cuda()
+        assert_close(f"top8[{step}]", g.logits[top], bf16_from_u16(arrays["top8_val"][step]))
+        if f"logits_step{step}" in arrays:
+            assert_close(f"logits[{step}]", g.logits, bf16_from_u16(arrays[f"logits_step{step}"]))
+            assert_close("k rows", model.stacked_kv_cache[0][:, 0, pos], bf16_from_u16(arrays[f"k_row_step{step}"]))
+            assert_close("v rows", model.stacked_kv_cache[1][:, 0, pos], bf16_from_u16(arrays[f"v_row_step{step}"]))
+        if int(out) != int(tokens[step + 1]):
+            mismatches.append((step, int(out), int(tokens[step + 1]), float(arrays["top2_margin"][step])))
+    assert_close("last layer k", model.stacked_kv_cache[0][-1, 0, n : n + meta["ntok"]], bf16_from_u16(arrays["last_layer_k_rows"]))
+    assert_close("last layer v", model.stacked_kv_cache[1][-1, 0, n : n + meta["ntok"]], bf16_from_u16(arrays["last_layer_v_rows"]))
+    print(f"worst |hidden err| {worst_hidden:.4f}, worst |logit err| {worst_logit:.4f}, "
+          f"mean exact fraction {np.mean(exact):.4f}, argmax mismatches {mismatches}")
+    # greedy tokens are equal wherever the oracle's own top-2 gap exceeds the logit tolerance
+    for step, got, want, margin in mismatches:
+        assert margin <= 2 * (3e-2 + 1e-2 * 8), (step, got, want, margin)
+    assert len(mismatches) <= 3
