@@ -158,7 +158,7 @@ def test_split_attention_with_reduction(partitions, context):
     from oracle import pyvm
     from thor_megakernels_b200.dispatch import make_mk_interpreter
 
-    cfg = dict(hidden_size=2048, num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+    cfg = dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
                intermediate_size=8192, vocab_size=4096)
     cpu_model = build_model(cfg, 1024, device="cpu", seed=3)
     model = build_model(cfg, 1024, device="cuda", seed=3)

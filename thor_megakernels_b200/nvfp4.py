@@ -1,0 +1,86 @@
+"""Host side of the NVFP4 weight-only path: quantise bf16 weights on the
+device and run the fused dequantise-GEMV, both through the C-ABI library.
+
+Storage follows the reference harness's ``Primitive.storage`` / ``quantize`` /
+``simt`` (tools/analysis/nvfp4/bench.py:58-84): ``packed`` uint8 ``[rows, k/2]``,
+``scales`` uint8 ``[rows, k/16]`` (E4M3 bits), ``tensor_scale`` =
+``max(amax / (6*448), 1e-12)``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+@dataclass
+class Nvfp4Weight:
+    packed: torch.Tensor        # uint8 [rows, k/2]
+    scales: torch.Tensor        # uint8 [rows, k/16]
+    tensor_scale: float
+    rows: int
+    k: int
+    decoded: torch.Tensor | None = None  # fp32 [rows, k], only when asked for
+
+    @property
+    def nbytes(self) -> int:
+        return self.packed.numel() + self.scales.numel()
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def tensor_scale_for(weight: torch.Tensor) -> float:
+    return float(np.float32(max(weight.abs().max().item() / (6 * 448), 1e-12)))
+
+
+def quantize_weight(weight: torch.Tensor, tensor_scale: float | None = None, reference: bool = False) -> Nvfp4Weight:
+    """Quantise a contiguous bf16 ``[rows, k]`` CUDA tensor (``k % 16 == 0``)."""
+    if weight.device.type != "cuda" or weight.dtype != torch.bfloat16 or not weight.is_contiguous() or weight.ndim != 2:
+        raise ValueError("Source must be contiguous device BF16 [rows, k]")
+    rows, k = weight.shape
+    if k % 16:
+        raise ValueError("k must be a multiple of 16")
+    ts = tensor_scale_for(weight) if tensor_scale is None else float(tensor_scale)
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=weight.device)
+    scales = torch.empty((rows, k // 16), dtype=torch.uint8, device=weight.device)
+    decoded = torch.empty((rows, k), dtype=torch.float32, device=weight.device) if reference else None
+    lib = _lib.load()
+    with torch.cuda.device(weight.device):
+        _lib.check(lib.mk_nvfp4_quantize(weight.data_ptr(), packed.data_ptr(), scales.data_ptr(),
+                                         decoded.data_ptr() if reference else None, rows, k, ts, _stream(weight)))
+    return Nvfp4Weight(packed, scales, ts, rows, k, decoded)
+
+
+def gemv(weight: Nvfp4Weight | torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``y[b] = W @ x[b]`` for ``x`` of shape ``[k]`` or ``[batch <= 8, k]`` (bf16),
+    fp32 accumulation, bf16 result.  ``weight`` is an ``Nvfp4Weight`` (fused
+    dequantisation) or a plain bf16 matrix."""
+    if x.device.type != "cuda" or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous bf16 CUDA tensor")
+    squeeze = x.ndim == 1
+    xb = x.view(1, -1) if squeeze else x
+    batch, k = xb.shape
+    is_packed = isinstance(weight, Nvfp4Weight)
+    rows = weight.rows if is_packed else weight.shape[0]
+    wk = weight.k if is_packed else weight.shape[1]
+    if wk != k:
+        raise ValueError(f"x has {k} columns, weight has {wk}")
+    y = out if out is not None else torch.empty((batch, rows), dtype=torch.bfloat16, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        if is_packed:
+            code = lib.mk_gemv(None, weight.packed.data_ptr(), weight.scales.data_ptr(), xb.data_ptr(), y.data_ptr(),
+                               rows, k, weight.tensor_scale, 1, batch, _stream(x))
+        else:
+            if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
+                raise ValueError("weight must be contiguous bf16")
+            code = lib.mk_gemv(weight.data_ptr(), None, None, xb.data_ptr(), y.data_ptr(), rows, k, 1.0, 0, batch,
+                               _stream(x))
+    if code != 0:
+        raise _lib.MegakernelError(code, f"mk_gemv refused m={rows} k={k} batch={batch}")
+    return y.view(-1) if squeeze and out is None else y
