@@ -21,12 +21,16 @@ MK_STEP_RESET_BARRIERS = 2
 MK_STEP_WRITE_TOKEN = 4
 MK_STEP_TIMINGS = 8
 
+MK_OPT_WAIT_BUDGET_CYCLES = 0
+MK_OPT_PREFETCH_STAGES = 1
+MK_OPT_PREFETCH_INTERVAL = 2
+
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1
 
 EXPORTED_SYMBOLS = [
     "mk_last_error", "mk_create", "mk_set_schedule", "mk_step", "mk_query", "mk_status",
-    "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof",
+    "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
 ]
 
 
@@ -103,6 +107,7 @@ def load() -> C.CDLL:
     lib.mk_nvfp4_quantize.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
     lib.mk_gemv.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
     lib.mk_abi_sizeof.argtypes = [i32]
+    lib.mk_set_option.argtypes = [vp, i32, C.c_int64]
     for name in EXPORTED_SYMBOLS:
         if name not in ("mk_last_error", "mk_destroy"):
             getattr(lib, name).restype = C.c_int

@@ -55,6 +55,8 @@ constexpr int kMaxHeadDim = 128;
 constexpr int kInstrWords = 32;
 constexpr int kTimingSlots = 128;
 constexpr int kConsumerBarrier = 1;                       // named barrier id
+constexpr int kSliceCounterRow = 7;                       // barriers[layer, 7, slice]: gate/up blocks done per 2048-column slice
+constexpr int kMaxDownSlices = 8;                         // intermediate_size <= 16384
 
 // timing slots (reference include/util.cuh:225-256)
 constexpr int kEvLoaderStart = 5, kEvStorerStart = 9, kEvConsumerStart = 11;
@@ -77,6 +79,8 @@ struct Params {
     unsigned flags;
     float attn_scale, eps;
     long long spin_cycles;
+    int prefetch_stages;        // 16 KiB stages the loader may request into L2 beyond the ring while the ring is full
+    long long prefetch_interval; // SM cycles between two such requests
     int down_slices;  // inter / 2048
     int down_total;   // (hidden / 16) * down_slices
     // weights
@@ -105,7 +109,7 @@ struct __align__(128) Smem {
     uint8_t stage[kStages][kStageBytes];
     float attn[kConsumerWarps][kGroup][kMaxHeadDim + 2];
     float partial[kPartialBufs][kConsumerWarps][kBlockRows];
-    float red[kConsumerWarps];
+    float red[2][kConsumerWarps];
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t pfull[kPartialBufs];
@@ -207,102 +211,190 @@ struct Ring {
     }
 };
 
-// Streams one 16-row x 2048-column tile as four 4-row stages.
-__device__ __forceinline__ void load_tile(const Params &p, Smem &s, Ring &ring, uint32_t &live, const bf16 *src,
-                                          size_t row_stride, uint64_t policy, int opcode, int slot) {
-    const uint8_t *base = reinterpret_cast<const uint8_t *>(src);
-    const size_t stride_bytes = row_stride * sizeof(bf16);
-#pragma unroll 1
-    for (int sub = 0; sub < kStagesPerTile; ++sub) {
-        wait_mbar(p, s, &s.empty[ring.stage], ring.phase ^ 1u, kFailRing, opcode, slot, (int)ring.stage);
-        if (aborted(s)) {
-            live &= ~(1u << ring.stage);
-        } else {
-            live |= 1u << ring.stage;
-            mbar_arrive_expect_tx(&s.full[ring.stage], kStageBytes);
-            const uint8_t *rows = base + (size_t)sub * kStageRows * stride_bytes;
-            if (stride_bytes == (size_t)kChunkCols * 2) {
-                bulk_load(s.stage[ring.stage], rows, kStageBytes, &s.full[ring.stage], policy);
-            } else {
-#pragma unroll
-                for (int r = 0; r < kStageRows; ++r)
-                    bulk_load(s.stage[ring.stage] + r * kChunkCols * 2, rows + r * stride_bytes, kChunkCols * 2,
-                              &s.full[ring.stage], policy);
+// One 16-row x 2048-column weight tile: first byte, row pitch, owning instruction.
+struct Tile {
+    const uint8_t *src;
+    size_t stride_bytes;
+    int opcode;
+    int slot;
+};
+
+// Walks a worker's instruction queue and yields its weight tiles in the order
+// the consumers use them.  Two cursors run over the same queue: one feeds the
+// shared-memory ring, one runs ahead of it issuing L2 prefetches.
+template <int NCH>
+struct TileCursor {
+    int slot = -1;
+    int op = 0;
+    int idx = 0, cnt = 0;   // block position within the instruction
+    int sub = 0, nsub = 1;  // tile position within the block
+    int first_block = 0;
+    const int *ins = nullptr;
+    const bf16 *base = nullptr, *base2 = nullptr;
+    size_t row_elems = 0;
+
+    __device__ __forceinline__ bool next(const Params &p, Tile &t) {
+        while (true) {
+            if (idx < cnt) {
+                const int block = (op == 5) ? __ldg(ins + 3 + idx) : first_block + idx;
+                const bf16 *w = (op == 5 && sub >= NCH) ? base2 : base;
+                const int chunk = (op == 6) ? 0 : (sub % NCH);
+                t.src = reinterpret_cast<const uint8_t *>(w + (size_t)block * kBlockRows * row_elems + chunk * kChunkCols);
+                t.stride_bytes = row_elems * sizeof(bf16);
+                t.opcode = op;
+                t.slot = slot;
+                if (++sub == nsub) { sub = 0; ++idx; }
+                return true;
             }
+            if (++slot >= p.queue_len) return false;
+            ins = instruction_at(p, slot);
+            op = __ldg(ins);
+            idx = 0; sub = 0; cnt = 0; nsub = NCH;
+            const size_t hidden = p.hidden;
+            switch (op) {
+            case 1: {
+                const int layer = __ldg(ins + 1);
+                first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block;
+                base = p.qkv_w + (size_t)layer * p.qkv_rows * hidden; row_elems = hidden;
+                break;
+            }
+            case 4: {
+                const int layer = __ldg(ins + 1);
+                first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block;
+                row_elems = (size_t)p.hq * p.hd;
+                base = p.o_w + (size_t)layer * hidden * row_elems;
+                break;
+            }
+            case 5: {
+                const int layer = __ldg(ins + 1);
+                cnt = __ldg(ins + 2); nsub = 2 * NCH;  // up tiles, then gate tiles
+                base = p.up_w + (size_t)layer * p.inter * hidden;
+                base2 = p.gate_w + (size_t)layer * p.inter * hidden;
+                row_elems = hidden;
+                break;
+            }
+            case 6: {
+                const int layer = __ldg(ins + 1);
+                first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block; nsub = 1;
+                row_elems = p.inter;
+                base = p.down_w + (size_t)layer * hidden * row_elems + (size_t)__ldg(ins + 4) * kChunkCols;
+                break;
+            }
+            case 7:
+                first_block = __ldg(ins + 1); cnt = __ldg(ins + 2) - first_block;
+                base = p.lm_w; row_elems = hidden;
+                break;
+            default:
+                break;  // attention ops, no-ops and unknown opcodes stream no weights
+            }
+            if (cnt < 0) cnt = 0;
         }
-        ring.advance();
     }
-}
+};
+
+// Position of a 4-row stage in a worker's tile stream.
+template <int NCH>
+struct StageCursor {
+    TileCursor<NCH> tiles;
+    Tile tile;
+    int sub = kStagesPerTile;  // forces a fetch on first use
+    long long index = 0;       // stages handed out so far
+    bool done = false;
+
+    // Moves to the next stage; false at the end of the queue.
+    __device__ __forceinline__ bool advance(const Params &p) {
+        if (done) return false;
+        if (sub + 1 < kStagesPerTile && index > 0) {
+            ++sub;
+        } else {
+            if (!tiles.next(p, tile)) { done = true; return false; }
+            sub = 0;
+        }
+        ++index;
+        return true;
+    }
+    __device__ __forceinline__ const uint8_t *rows() const {
+        return tile.src + (size_t)sub * kStageRows * tile.stride_bytes;
+    }
+};
 
 template <int NCH>
 __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
     const uint64_t policy = l2_evict_first_policy();
     Ring ring;
-    const size_t hidden = p.hidden;
     uint32_t live = 0;  // stages whose most recent fill was actually issued
-#pragma unroll 1
-    for (int slot = 0; slot < p.queue_len; ++slot) {
-        const int *ins = instruction_at(p, slot);
-        const int op = __ldg(ins);
-        if (op == 0) continue;
-        stamp(p, slot, kEvLoaderStart, t_start);
-        switch (op) {
-        case 1: {
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
-            const bf16 *w = p.qkv_w + (size_t)layer * p.qkv_rows * hidden;
-            for (int b = b0; b < b1; ++b)
-                for (int c = 0; c < NCH; ++c) {
-                    load_tile(p, s, ring, live, w + (size_t)b * kBlockRows * hidden + c * kChunkCols, hidden, policy, op, slot);
-                }
-            break;
+    StageCursor<NCH> fill, ahead;
+    long long last_prefetch = clock64();
+    int last_slot = -1;
+
+    while (fill.advance(p)) {
+        const Tile &t = fill.tile;
+        if (t.slot != last_slot) {
+            if (last_slot >= 0) stamp(p, last_slot, kEvLastLoad, t_start);
+            stamp(p, t.slot, kEvLoaderStart, t_start);
+            last_slot = t.slot;
         }
-        case 4: {
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
-            const size_t k = (size_t)p.hq * p.hd;
-            const bf16 *w = p.o_w + (size_t)layer * hidden * k;
-            for (int b = b0; b < b1; ++b)
-                for (int c = 0; c < NCH; ++c) {
-                    load_tile(p, s, ring, live, w + (size_t)b * kBlockRows * k + c * kChunkCols, k, policy, op, slot);
+        // Wait for a free ring stage.  While the ring is full the loader would
+        // idle, and so would HBM: use the time to ask L2 for the stages that
+        // come next, one stage per `prefetch_interval` cycles so that this SM's
+        // latency-critical activation loads never queue behind a large burst.
+        uint64_t *slot_free = &s.empty[ring.stage];
+        const uint32_t parity = ring.phase ^ 1u;
+        if (!mbar_try_wait(slot_free, parity) && !aborted(s)) {
+            const long long t0 = clock64();
+            unsigned it = 0;
+            while (!mbar_try_wait(slot_free, parity)) {
+                const long long now = clock64();
+                if (p.prefetch_stages > 0 && now - last_prefetch >= p.prefetch_interval) {
+                    while (!ahead.done && ahead.index < fill.index) ahead.advance(p);  // catch up, nothing to fetch
+                    if (!ahead.done && ahead.index - fill.index < p.prefetch_stages) {
+                        // `ahead` sits on the stage the ring is waiting to take (or beyond it)
+                        if (ahead.index == 0) ahead.advance(p);
+                        if (!ahead.done) {
+                            const uint8_t *rows = ahead.rows();
+                            if (ahead.tile.stride_bytes == (size_t)kChunkCols * 2) {
+                                bulk_prefetch_l2(rows, kStageBytes);
+                            } else {
+#pragma unroll
+                                for (int r = 0; r < kStageRows; ++r)
+                                    bulk_prefetch_l2(rows + r * ahead.tile.stride_bytes, kChunkCols * 2);
+                            }
+                            ahead.advance(p);
+                            last_prefetch = now;
+                        }
+                    }
                 }
-            break;
-        }
-        case 5: {
-            const int layer = __ldg(ins + 1), n = __ldg(ins + 2);
-            const bf16 *up = p.up_w + (size_t)layer * p.inter * hidden;
-            const bf16 *gate = p.gate_w + (size_t)layer * p.inter * hidden;
-            for (int i = 0; i < n; ++i) {
-                const int b = __ldg(ins + 3 + i);
-                for (int c = 0; c < NCH; ++c) {
-                    load_tile(p, s, ring, live, up + (size_t)b * kBlockRows * hidden + c * kChunkCols, hidden, policy, op, slot);
-                }
-                for (int c = 0; c < NCH; ++c) {
-                    load_tile(p, s, ring, live, gate + (size_t)b * kBlockRows * hidden + c * kChunkCols, hidden, policy, op, slot);
+                if ((++it & 31u) == 0) {
+                    if (aborted(s)) break;
+                    if ((it & 1023u) == 0 && ld_relaxed_gpu(&p.status[7]) != 0) {
+                        *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+                        break;
+                    }
+                    if (now - t0 > p.spin_cycles) {
+                        report_failure(p, s, kFailRing, t.opcode, t.slot, (int)ring.stage, (int)parity);
+                        break;
+                    }
                 }
             }
-            break;
         }
-        case 6: {
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
-            const size_t k = p.inter;
-            const bf16 *w = p.down_w + (size_t)layer * hidden * k + (size_t)red * kChunkCols;
-            for (int b = b0; b < b1; ++b) {
-                load_tile(p, s, ring, live, w + (size_t)b * kBlockRows * k, k, policy, op, slot);
+        if (aborted(s)) {
+            live &= ~(1u << ring.stage);
+        } else {
+            live |= 1u << ring.stage;
+            mbar_arrive_expect_tx(&s.full[ring.stage], kStageBytes);
+            const uint8_t *rows = fill.rows();
+            if (t.stride_bytes == (size_t)kChunkCols * 2) {
+                bulk_load(s.stage[ring.stage], rows, kStageBytes, &s.full[ring.stage], policy);
+            } else {
+#pragma unroll
+                for (int r = 0; r < kStageRows; ++r)
+                    bulk_load(s.stage[ring.stage] + r * kChunkCols * 2, rows + r * t.stride_bytes, kChunkCols * 2,
+                              &s.full[ring.stage], policy);
             }
-            break;
         }
-        case 7: {
-            const int b0 = __ldg(ins + 1), b1 = __ldg(ins + 2);
-            for (int b = b0; b < b1; ++b)
-                for (int c = 0; c < NCH; ++c) {
-                    load_tile(p, s, ring, live, p.lm_w + (size_t)b * kBlockRows * hidden + c * kChunkCols, hidden, policy, op, slot);
-                }
-            break;
-        }
-        default:
-            break;  // attention ops and unknown opcodes stream no weights
-        }
-        stamp(p, slot, kEvLastLoad, t_start);
+        ring.advance();
     }
+    if (last_slot >= 0) stamp(p, last_slot, kEvLastLoad, t_start);
     // Never leave the CTA with copies in flight.  In a clean run every fill has
     // been waited for by the consumers; when aborting, wait here (bounded,
     // ignoring the abort flag) for the last fill of every stage.
@@ -326,6 +418,7 @@ struct ConsumerState {
     Ring ring;
     uint32_t pbuf = 0;
     uint32_t pphase = 0;
+    uint32_t norm_toggle = 0;
     __device__ __forceinline__ void advance_partial() {
         if (++pbuf == kPartialBufs) { pbuf = 0; pphase ^= 1u; }
     }
@@ -344,15 +437,31 @@ __device__ __forceinline__ void consumer_wait(const Params &p, Smem &s, int ctid
 // time, each add rounded to bf16, which is the order and rounding of the
 // reference interpreter's sequential `hidden += partial` updates.
 __device__ __forceinline__ void load_hidden8(const Params &p, const bf16 *base, bool merge, int idx, float (&h)[8]) {
-    ldcg8(base + idx, h);
-    if (merge) {
-        for (int sl = 0; sl < p.down_slices; ++sl) {
-            float part[8];
-            ldcg8(p.down_partials + (size_t)sl * p.hidden + idx, part);
+    const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(base + idx));
+    if (!merge) {
+        unpack8(raw, h);
+        return;
+    }
+    // slices in groups of four: all loads of a group are issued before its dependent adds
+    bool first = true;
+    for (int s0 = 0; s0 < p.down_slices; s0 += 4) {
+        uint4 parts[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) h[i] = round_bf16(h[i] + part[i]);
+        for (int j = 0; j < 4; ++j)
+            if (s0 + j < p.down_slices)
+                parts[j] = __ldcg(reinterpret_cast<const uint4 *>(p.down_partials + (size_t)(s0 + j) * p.hidden + idx));
+        if (first) { unpack8(raw, h); first = false; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (s0 + j < p.down_slices) {
+                float part[8];
+                unpack8(parts[j], part);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) h[i] = round_bf16(h[i] + part[i]);
+            }
         }
     }
+    if (first) unpack8(raw, h);
 }
 
 // RMSNorm of the residual stream into registers: thread `ctid` keeps elements
@@ -360,9 +469,12 @@ __device__ __forceinline__ void load_hidden8(const Params &p, const bf16 *base, 
 // rounded to bf16 and then multiplied by the bf16 weight with a second rounding
 // (reference python_vm.py:50-56).
 template <int NCH>
-__device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, const bf16 *base, bool merge,
-                                            const bf16 *norm_w, float (&x)[NCH][8]) {
+__device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, uint32_t &toggle, const bf16 *base,
+                                            bool merge, const bf16 *norm_w, float (&x)[NCH][8]) {
     const int lane = ctid & 31, cw = ctid >> 5;
+    uint4 wraw[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) wraw[c] = __ldg(reinterpret_cast<const uint4 *>(norm_w + c * kChunkCols + ctid * 8));
     float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
@@ -372,18 +484,20 @@ __device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, 
     }
 #pragma unroll
     for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-    if (lane == 0) s.red[cw] = ss;
+    // Two scratch rows used alternately: a row is rewritten only after the
+    // barrier of the following call, which every reader of it has passed.
+    float *red = s.red[toggle];
+    toggle ^= 1u;
+    if (lane == 0) red[cw] = ss;
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
     float total = 0.f;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) total += s.red[w];
-    named_barrier_sync(kConsumerBarrier, kConsumerThreads);  // s.red may be rewritten after this
+    for (int w = 0; w < kConsumerWarps; ++w) total += red[w];
     const float rstd = 1.0f / sqrtf(total / (float)p.hidden + p.eps);
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
         float w[8];
-        uint4 raw = __ldg(reinterpret_cast<const uint4 *>(norm_w + c * kChunkCols + ctid * 8));
-        unpack8(raw, w);
+        unpack8(wraw[c], w);
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[c][i] = round_bf16(w[i] * round_bf16(x[c][i] * rstd));
     }
@@ -438,16 +552,6 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
     const int D = p.hd;
     const int blocks_per_head = D / kBlockRows;
 
-    if (ctid == 0) {
-        stamp(p, slot, kEvAtWait, t_start);
-        for (int i = 0; i < kGroup; ++i)
-            wait_counter(p, s, counter(p, layer, 0, kv_head * kGroup + i), blocks_per_head, 2, slot);
-        wait_counter(p, s, counter(p, layer, 0, p.hq + kv_head), blocks_per_head, 2, slot);
-        wait_counter(p, s, counter(p, layer, 0, p.hq + p.hkv + kv_head), blocks_per_head, 2, slot);
-        stamp(p, slot, kEvDoneWait, t_start);
-    }
-    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
-
     const int seq_len = p.pos + 1;
     const int total_blocks = (seq_len + 15) / 16;
     const int per_partial = (total_blocks + num_partials - 1) / num_partials;
@@ -463,10 +567,48 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
     const int sub = lane % lanes_per_tok;
     const int tslot = lane / lanes_per_tok;
     const int d0 = sub * 8;
+    const size_t tok_stride = (size_t)p.hkv * D;
+    const size_t layer_off = (size_t)layer * p.kv_batch * p.kv_len * tok_stride + (size_t)kv_head * D + d0;
+    const bf16 *kbase = p.k_cache + layer_off;
+    const bf16 *vbase = p.v_cache + layer_off;
+    const int stride_toks = kConsumerWarps * toks_per_warp;
+    const int my_first = t0 + cw * toks_per_warp + tslot;
 
-    float q[kGroup][8];
+    // Rows below the current position were written by earlier launches: fetch the
+    // first two iterations' worth while the Q/K/V producers are still running.
+    uint4 k_now = make_uint4(0u, 0u, 0u, 0u), v_now = k_now, k_next = k_now, v_next = k_now;
+    if (my_first < t1 && my_first < p.pos) {
+        k_now = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)my_first * tok_stride));
+        v_now = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)my_first * tok_stride));
+    }
+    if (my_first + stride_toks < t1 && my_first + stride_toks < p.pos) {
+        k_next = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)(my_first + stride_toks) * tok_stride));
+        v_next = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)(my_first + stride_toks) * tok_stride));
+    }
+
+    if (ctid == 0) {
+        stamp(p, slot, kEvAtWait, t_start);
+        for (int i = 0; i < kGroup; ++i)
+            wait_counter(p, s, counter(p, layer, 0, kv_head * kGroup + i), blocks_per_head, 2, slot);
+        wait_counter(p, s, counter(p, layer, 0, p.hq + kv_head), blocks_per_head, 2, slot);
+        wait_counter(p, s, counter(p, layer, 0, p.hq + p.hkv + kv_head), blocks_per_head, 2, slot);
+        stamp(p, slot, kEvDoneWait, t_start);
+    }
+    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
+
+    uint4 q[kGroup];  // kept packed (bf16 pairs) to save registers
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) ldcg8(p.q_post + (size_t)(kv_head * kGroup + h) * D + d0, q[h]);
+    for (int h = 0; h < kGroup; ++h)
+        q[h] = __ldcg(reinterpret_cast<const uint4 *>(p.q_post + (size_t)(kv_head * kGroup + h) * D + d0));
+    // the row appended by this launch, if it is one of the two fetched early
+    if (my_first < t1 && my_first >= p.pos) {
+        k_now = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)my_first * tok_stride));
+        v_now = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)my_first * tok_stride));
+    }
+    if (my_first + stride_toks < t1 && my_first + stride_toks >= p.pos) {
+        k_next = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)(my_first + stride_toks) * tok_stride));
+        v_next = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)(my_first + stride_toks) * tok_stride));
+    }
 
     float m[kGroup], l[kGroup], acc[kGroup][8];
 #pragma unroll
@@ -476,39 +618,35 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
     }
+    const float scale_log2e = p.attn_scale * 1.4426950408889634f;  // softmax in base 2; m[] is in log2 units
 
-    const size_t tok_stride = (size_t)p.hkv * D;
-    const size_t layer_off = (size_t)layer * p.kv_batch * p.kv_len * tok_stride + (size_t)kv_head * D + d0;
-    const bf16 *kbase = p.k_cache + layer_off;
-    const bf16 *vbase = p.v_cache + layer_off;
-    const int stride_toks = kConsumerWarps * toks_per_warp;
-
-    for (int tb = t0; tb < t1; tb += stride_toks) {
+#pragma unroll 1
+    for (int tb = t0; tb < t1; tb += stride_toks) {  // warp-uniform trip count
         const int t = tb + cw * toks_per_warp + tslot;
-        const bool valid = t < t1;
-        float kf[8], vf[8];
-        if (valid) {
-            ldcg8(kbase + (size_t)t * tok_stride, kf);
-            ldcg8(vbase + (size_t)t * tok_stride, vf);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) kf[i] = vf[i] = 0.f;
+        const uint4 kraw = k_now, vraw = v_now;
+        k_now = k_next;
+        v_now = v_next;
+        const int t2 = t + 2 * stride_toks;  // two iterations of loads stay in flight
+        if (t2 < t1) {
+            k_next = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)t2 * tok_stride));
+            v_next = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)t2 * tok_stride));
         }
+        float kf[8], vf[8];
+        unpack8(kraw, kf);
+        unpack8(vraw, vf);
         float sc[kGroup];
 #pragma unroll
         for (int h = 0; h < kGroup; ++h) {
-            float d = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) d = fmaf(q[h][i], kf[i], d);
+            float d = dot8(q[h], kf, 0.f);
             for (int off = 1; off < lanes_per_tok; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-            sc[h] = d * p.attn_scale;
+            sc[h] = d * scale_log2e;
         }
-        if (valid) {
+        if (t < t1) {
 #pragma unroll
             for (int h = 0; h < kGroup; ++h) {
                 const float mn = fmaxf(m[h], sc[h]);
-                const float corr = expf(m[h] - mn);  // exp(-inf) = 0 on the first row
-                const float pr = expf(sc[h] - mn);
+                const float corr = exp2f(m[h] - mn);  // exp2(-inf) = 0 on the first row
+                const float pr = exp2f(sc[h] - mn);
                 l[h] = l[h] * corr + pr;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(pr, vf[i], acc[h][i] * corr);
@@ -524,8 +662,8 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
             const float mo = __shfl_xor_sync(0xffffffffu, m[h], off);
             const float lo = __shfl_xor_sync(0xffffffffu, l[h], off);
             const float mn = fmaxf(m[h], mo);
-            const float ca = (m[h] == -INFINITY) ? 0.f : expf(m[h] - mn);
-            const float cb = (mo == -INFINITY) ? 0.f : expf(mo - mn);
+            const float ca = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - mn);
+            const float cb = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
             l[h] = l[h] * ca + lo * cb;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -558,7 +696,7 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) {
             const float mw = s.attn[w][h][kMaxHeadDim];
-            const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
             L = fmaf(s.attn[w][h][kMaxHeadDim + 1], f, L);
             O = fmaf(s.attn[w][h][d], f, O);
         }
@@ -569,10 +707,9 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
                 p.attn_out[(size_t)head * D + d] = __float2bfloat16_rn(out);
             } else {
                 p.attn_oi[((size_t)head * p.max_partials + part) * D + d] = out;
-                // log2 of the natural-exponent sum (reference python_vm.py:323)
+                // log2 of the natural-exponent sum (reference python_vm.py:323); M is already in log2 units
                 if (d == 0)
-                    p.attn_lse[(size_t)head * p.max_partials + part] =
-                        (L > 0.f) ? M * 1.4426950408889634f + log2f(L) : -INFINITY;
+                    p.attn_lse[(size_t)head * p.max_partials + part] = (L > 0.f) ? M + log2f(L) : -INFINITY;
             }
         }
     }
@@ -581,7 +718,8 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
         if (p.skip_attn_reduction) {
             red_release_gpu_add(counter(p, layer, 2, 0), kGroup);
         } else {
-            for (int h = 0; h < kGroup; ++h) red_release_gpu_add(counter(p, layer, 1, kv_head * kGroup + h), 1);
+            fence_acq_rel_gpu();
+            for (int h = 0; h < kGroup; ++h) red_relaxed_gpu_add(counter(p, layer, 1, kv_head * kGroup + h), 1);
         }
         stamp(p, slot, kEvOutputReady, t_start);
     }
@@ -655,7 +793,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
                 if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
             }
             const bf16 *base = (layer == 0 && token_row) ? token_row : p.hidden_states;
-            load_normed<NCH>(p, s, ctid, base, layer > 0, p.attn_norm_w + (size_t)layer * p.hidden, x);
+            load_normed<NCH>(p, s, ctid, st.norm_toggle, base, layer > 0, p.attn_norm_w + (size_t)layer * p.hidden, x);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
             for (int b = b0; b < b1; ++b) consume_block<NCH>(p, s, st, lane, cw, x, op, slot);
             break;
@@ -681,7 +819,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, layer, 3, 0), p.hidden / kBlockRows, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-            load_normed<NCH>(p, s, ctid, p.hidden_states, false, p.mlp_norm_w + (size_t)layer * p.hidden, x);
+            load_normed<NCH>(p, s, ctid, st.norm_toggle, p.hidden_states, false, p.mlp_norm_w + (size_t)layer * p.hidden, x);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
             for (int i = 0; i < n; ++i) {
                 consume_block<NCH>(p, s, st, lane, cw, x, op, slot);  // up rows
@@ -692,7 +830,8 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
         case 6: {
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
-            consumer_wait(p, s, ctid, counter(p, layer, 4, 0), p.inter / kBlockRows, op, slot);
+            // only the gate/up rows of this 2048-column slice have to be ready
+            consumer_wait(p, s, ctid, counter(p, layer, kSliceCounterRow, red), kChunkCols / kBlockRows, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
             float xs[1][8];
             load_plain<1>(p.silu_out + (size_t)red * kChunkCols, ctid, xs);
@@ -705,7 +844,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, p.layers - 1, 5, 0), p.down_total, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-            load_normed<NCH>(p, s, ctid, p.hidden_states, true, p.lm_norm_w, x);
+            load_normed<NCH>(p, s, ctid, st.norm_toggle, p.hidden_states, true, p.lm_norm_w, x);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
             for (int b = b0; b < b1; ++b) consume_block<NCH>(p, s, st, lane, cw, x, op, slot);
             break;
@@ -796,7 +935,16 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                     else if (row < v_start) p.k_cache[cache_row + (row - k_start)] = o;
                     else p.v_cache[cache_row + (row - v_start)] = o;
                 }
-                publish(p, s, lane, counter(p, layer, 0, b / (D / kBlockRows)), 1);
+            }
+            // one counter per head; the first release also covers the later heads' rows
+            const int bph = D / kBlockRows;
+            __syncwarp();
+            if (lane == 0 && !aborted(s)) {
+                fence_acq_rel_gpu();  // once; the adds below are relaxed
+                for (int head = b0 / bph; head <= (b1 - 1) / bph; ++head) {
+                    const int lo = max(b0, head * bph), hi = min(b1, (head + 1) * bph);
+                    red_relaxed_gpu_add(counter(p, layer, 0, head), hi - lo);
+                }
             }
             break;
         }
@@ -814,8 +962,8 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                             h = round_bf16(h + ldcg_bf16(p.down_partials + (size_t)sl * p.hidden + row));
                     p.hidden_states[row] = __float2bfloat16_rn(h + y);
                 }
-                publish(p, s, lane, counter(p, layer, 3, 0), 1);
             }
+            publish(p, s, lane, counter(p, layer, 3, 0), b1 - b0);
             break;
         }
         case 5: {
@@ -829,8 +977,17 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                     const float act = round_bf16(gate / (1.0f + expf(-gate)));
                     p.silu_out[b * kBlockRows + lane] = __float2bfloat16_rn(act * up);
                 }
-                publish(p, s, lane, counter(p, layer, 4, 0), 1);
             }
+            // per 2048-column slice of silu_out (what one down-projection
+            // instruction reads), then the reference interpreter's single counter
+            const int my_slice = lane < n ? (__ldg(ins + 3 + lane) * kBlockRows) / kChunkCols : -1;
+            __syncwarp();
+            if (lane == 0) fence_acq_rel_gpu();  // once; the adds below are relaxed
+            for (int sl = 0; sl < p.down_slices; ++sl) {
+                const int cnt = __popc(__ballot_sync(0xffffffffu, my_slice == sl));
+                if (lane == 0 && cnt && !aborted(s)) red_relaxed_gpu_add(counter(p, layer, kSliceCounterRow, sl), cnt);
+            }
+            if (lane == 0 && !aborted(s)) red_relaxed_gpu_add(counter(p, layer, 4, 0), n);
             break;
         }
         case 6: {
@@ -841,8 +998,8 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                 const float y = collect_block(p, s, st, lane, op, slot);
                 if (lane < kBlockRows && !aborted(s))
                     p.down_partials[(size_t)red * p.hidden + b * kBlockRows + lane] = __float2bfloat16_rn(y);
-                publish(p, s, lane, counter(p, layer, 5, 0), 1);
             }
+            publish(p, s, lane, counter(p, layer, 5, 0), b1 - b0);
             break;
         }
         case 7: {
@@ -1079,6 +1236,8 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.skip_attn_reduction = d->skip_attn_reduction;
     p.attn_scale = d->attn_scale; p.eps = d->rms_norm_eps;
     p.spin_cycles = 4000000000ll;
+    p.prefetch_stages = 0;  // measured slower than the ring alone on B200; kept as an option
+    p.prefetch_interval = 700;
     p.down_slices = slices;
     p.down_total = (H / kBlockRows) * slices;
     p.qkv_w = (const bf16 *)d->qkv_w; p.attn_norm_w = (const bf16 *)d->attn_norm_w; p.o_w = (const bf16 *)d->o_w;
@@ -1191,6 +1350,27 @@ extern "C" int mk_set_wait_budget(void *handle, int64_t cycles) {
     if (!h || cycles <= 0) return fail(MK_ERR_BAD_ARGUMENT, "mk_set_wait_budget: bad argument");
     h->params.spin_cycles = cycles;
     return 0;
+}
+
+extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
+    Handle *h = (Handle *)handle;
+    if (!h) return fail(MK_ERR_BAD_ARGUMENT, "mk_set_option: null handle");
+    switch (option) {
+    case MK_OPT_WAIT_BUDGET_CYCLES:
+        if (value <= 0) return fail(MK_ERR_BAD_ARGUMENT, "wait budget must be positive");
+        h->params.spin_cycles = value;
+        return 0;
+    case MK_OPT_PREFETCH_STAGES:
+        if (value < 0 || value > 256) return fail(MK_ERR_BAD_ARGUMENT, "prefetch distance must be 0..256 stages");
+        h->params.prefetch_stages = (int)value;
+        return 0;
+    case MK_OPT_PREFETCH_INTERVAL:
+        if (value < 0) return fail(MK_ERR_BAD_ARGUMENT, "prefetch interval must not be negative");
+        h->params.prefetch_interval = value;
+        return 0;
+    default:
+        return fail(MK_ERR_BAD_ARGUMENT, "mk_set_option: unknown option %d", option);
+    }
 }
 
 extern "C" void mk_destroy(void *handle) {

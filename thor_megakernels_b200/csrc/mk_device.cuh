@@ -67,6 +67,13 @@ __device__ __forceinline__ void bulk_load(void *dst_smem, const void *src_gmem, 
         : "memory");
 }
 
+// Asks L2 to fetch `bytes` (multiple of 16) starting at a 16-byte aligned
+// global address; nothing is written to shared memory and nothing signals
+// completion.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src_gmem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
+
 // Every lane of every participating warp must call this; the warp is
 // reconverged first because lanes may arrive from a single-lane polling loop.
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
@@ -95,6 +102,13 @@ __device__ __forceinline__ int ld_relaxed_gpu(const int *p) {
 // acquires the counter.
 __device__ __forceinline__ void red_release_gpu_add(int *p, int v) {
     asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
+// Only after fence_acq_rel_gpu() by the same thread: fence + relaxed add is a release.
+__device__ __forceinline__ void red_relaxed_gpu_add(int *p, int v) {
+    asm volatile("red.relaxed.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // ---------------------------------------------------------------------------

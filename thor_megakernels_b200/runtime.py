@@ -188,6 +188,9 @@ class Megakernel:
     def set_wait_budget(self, cycles: int):
         _lib.check(self.lib.mk_set_wait_budget(self.handle, int(cycles)))
 
+    def set_option(self, option: int, value: int):
+        _lib.check(self.lib.mk_set_option(self.handle, int(option), int(value)))
+
     def close(self):
         if getattr(self, "handle", None) is not None and self.handle.value:
             self.lib.mk_destroy(self.handle)
