@@ -202,9 +202,6 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
 /* Tuning knobs without a counterpart in the reference (its equivalents are
  * compile-time constants, include/config.cuh:7-72). */
 #define MK_OPT_WAIT_BUDGET_CYCLES 0  /* same as mk_set_wait_budget */
-#define MK_OPT_PREFETCH_STAGES    1  /* 16 KiB weight stages the loader may request into L2 beyond the
-                                        shared-memory ring while the ring is full (default 0 = off) */
-#define MK_OPT_PREFETCH_INTERVAL  2  /* SM cycles between two such requests per SM (default 700) */
 int mk_set_option(void *handle, int32_t option, int64_t value);
 
 void mk_destroy(void *handle);

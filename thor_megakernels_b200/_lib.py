@@ -22,8 +22,6 @@ MK_STEP_WRITE_TOKEN = 4
 MK_STEP_TIMINGS = 8
 
 MK_OPT_WAIT_BUDGET_CYCLES = 0
-MK_OPT_PREFETCH_STAGES = 1
-MK_OPT_PREFETCH_INTERVAL = 2
 
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1

@@ -41,10 +41,13 @@ namespace mk {
 // ---------------------------------------------------------------------------
 constexpr int kBlockRows = 16;                            // output rows per block
 constexpr int kChunkCols = 2048;                          // input columns per tile
-constexpr int kStageRows = 4;                             // rows per ring stage
-constexpr int kStageBytes = kStageRows * kChunkCols * 2;  // 16 KiB
-constexpr int kStagesPerTile = kBlockRows / kStageRows;   // 4
-constexpr int kStages = 12;                               // 192 KiB ring
+constexpr int kRowBytes = kChunkCols * 2;                 // 4 KiB of a weight row per tile
+// Rows sit 64 bytes further apart than their length so that the two rows an
+// 8-lane shared-memory access phase touches fall into different bank halves.
+constexpr int kRowPitch = kRowBytes + 64;
+constexpr int kTileBytes = kBlockRows * kRowBytes;        // 64 KiB moved per tile
+constexpr int kStageBytes = kBlockRows * kRowPitch;       // shared-memory footprint of a tile
+constexpr int kStages = 3;                                // tiles in flight per SM (192 KiB)
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = (1 + kConsumerWarps + 1) * 32;   // loader + consumers + storer
@@ -79,8 +82,6 @@ struct Params {
     unsigned flags;
     float attn_scale, eps;
     long long spin_cycles;
-    int prefetch_stages;        // 16 KiB stages the loader may request into L2 beyond the ring while the ring is full
-    long long prefetch_interval; // SM cycles between two such requests
     int down_slices;  // inter / 2048
     int down_total;   // (hidden / 16) * down_slices
     // weights
@@ -110,6 +111,7 @@ struct __align__(128) Smem {
     float attn[kConsumerWarps][kGroup][kMaxHeadDim + 2];
     float partial[kPartialBufs][kConsumerWarps][kBlockRows];
     float red[2][kConsumerWarps];
+    __align__(16) bf16 xbuf[2 * kChunkCols];  // normalised activations, re-read in the MMA operand layout
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t pfull[kPartialBufs];
@@ -220,8 +222,7 @@ struct Tile {
 };
 
 // Walks a worker's instruction queue and yields its weight tiles in the order
-// the consumers use them.  Two cursors run over the same queue: one feeds the
-// shared-memory ring, one runs ahead of it issuing L2 prefetches.
+// the consumers use them.
 template <int NCH>
 struct TileCursor {
     int slot = -1;
@@ -292,105 +293,30 @@ struct TileCursor {
     }
 };
 
-// Position of a 4-row stage in a worker's tile stream.
-template <int NCH>
-struct StageCursor {
-    TileCursor<NCH> tiles;
-    Tile tile;
-    int sub = kStagesPerTile;  // forces a fetch on first use
-    long long index = 0;       // stages handed out so far
-    bool done = false;
-
-    // Moves to the next stage; false at the end of the queue.
-    __device__ __forceinline__ bool advance(const Params &p) {
-        if (done) return false;
-        if (sub + 1 < kStagesPerTile && index > 0) {
-            ++sub;
-        } else {
-            if (!tiles.next(p, tile)) { done = true; return false; }
-            sub = 0;
-        }
-        ++index;
-        return true;
-    }
-    __device__ __forceinline__ const uint8_t *rows() const {
-        return tile.src + (size_t)sub * kStageRows * tile.stride_bytes;
-    }
-};
-
 template <int NCH>
 __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
     const uint64_t policy = l2_evict_first_policy();
     Ring ring;
     uint32_t live = 0;  // stages whose most recent fill was actually issued
-    StageCursor<NCH> fill, ahead;
-    long long last_prefetch = clock64();
+    TileCursor<NCH> tiles;
+    Tile t;
     int last_slot = -1;
-
-    while (fill.advance(p)) {
-        const Tile &t = fill.tile;
+    while (tiles.next(p, t)) {
         if (t.slot != last_slot) {
             if (last_slot >= 0) stamp(p, last_slot, kEvLastLoad, t_start);
             stamp(p, t.slot, kEvLoaderStart, t_start);
             last_slot = t.slot;
         }
-        // Wait for a free ring stage.  While the ring is full the loader would
-        // idle, and so would HBM: use the time to ask L2 for the stages that
-        // come next, one stage per `prefetch_interval` cycles so that this SM's
-        // latency-critical activation loads never queue behind a large burst.
-        uint64_t *slot_free = &s.empty[ring.stage];
-        const uint32_t parity = ring.phase ^ 1u;
-        if (!mbar_try_wait(slot_free, parity) && !aborted(s)) {
-            const long long t0 = clock64();
-            unsigned it = 0;
-            while (!mbar_try_wait(slot_free, parity)) {
-                const long long now = clock64();
-                if (p.prefetch_stages > 0 && now - last_prefetch >= p.prefetch_interval) {
-                    while (!ahead.done && ahead.index < fill.index) ahead.advance(p);  // catch up, nothing to fetch
-                    if (!ahead.done && ahead.index - fill.index < p.prefetch_stages) {
-                        // `ahead` sits on the stage the ring is waiting to take (or beyond it)
-                        if (ahead.index == 0) ahead.advance(p);
-                        if (!ahead.done) {
-                            const uint8_t *rows = ahead.rows();
-                            if (ahead.tile.stride_bytes == (size_t)kChunkCols * 2) {
-                                bulk_prefetch_l2(rows, kStageBytes);
-                            } else {
-#pragma unroll
-                                for (int r = 0; r < kStageRows; ++r)
-                                    bulk_prefetch_l2(rows + r * ahead.tile.stride_bytes, kChunkCols * 2);
-                            }
-                            ahead.advance(p);
-                            last_prefetch = now;
-                        }
-                    }
-                }
-                if ((++it & 31u) == 0) {
-                    if (aborted(s)) break;
-                    if ((it & 1023u) == 0 && ld_relaxed_gpu(&p.status[7]) != 0) {
-                        *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
-                        break;
-                    }
-                    if (now - t0 > p.spin_cycles) {
-                        report_failure(p, s, kFailRing, t.opcode, t.slot, (int)ring.stage, (int)parity);
-                        break;
-                    }
-                }
-            }
-        }
+        wait_mbar(p, s, &s.empty[ring.stage], ring.phase ^ 1u, kFailRing, t.opcode, t.slot, (int)ring.stage);
         if (aborted(s)) {
             live &= ~(1u << ring.stage);
         } else {
             live |= 1u << ring.stage;
-            mbar_arrive_expect_tx(&s.full[ring.stage], kStageBytes);
-            const uint8_t *rows = fill.rows();
-            if (t.stride_bytes == (size_t)kChunkCols * 2) {
-                bulk_load(s.stage[ring.stage], rows, kStageBytes, &s.full[ring.stage], policy);
-            } else {
-#pragma unroll
-                for (int r = 0; r < kStageRows; ++r)
-                    bulk_load(s.stage[ring.stage] + r * kChunkCols * 2, rows + r * t.stride_bytes, kChunkCols * 2,
-                              &s.full[ring.stage], policy);
-            }
+            mbar_arrive_expect_tx(&s.full[ring.stage], kTileBytes);
+            uint8_t *dst = s.stage[ring.stage];
+#pragma unroll 4
+            for (int r = 0; r < kBlockRows; ++r)
+                bulk_load(dst + r * kRowPitch, t.src + r * t.stride_bytes, kRowBytes, &s.full[ring.stage], policy);
         }
         ring.advance();
     }
@@ -464,23 +390,38 @@ __device__ __forceinline__ void load_hidden8(const Params &p, const bf16 *base, 
     if (first) unpack8(raw, h);
 }
 
-// RMSNorm of the residual stream into registers: thread `ctid` keeps elements
-// [c*2048 + ctid*8, +8) of chunk c.  fp32 statistics; the normalised value is
-// rounded to bf16 and then multiplied by the bf16 weight with a second rounding
-// (reference python_vm.py:50-56).
+// Activation operand of the tensor-core matvec.  Consumer warp `cw` owns input
+// columns [cw*256, +256) of every 2048-column chunk; within the warp, lane
+// (g = lane/4, t = lane%4) holds for j = 0..7 the eight bf16 values of columns
+// cw*256 + j*32 + t*8 .. +7 (one uint4).  All eight g-groups hold the same
+// values: the MMA's eight output columns are copies and only column 0 is kept.
+template <int NCH>
+using XOperand = uint4[NCH][8];
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    // both inputs already hold bf16-representable values
+    return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);
+}
+
+// RMSNorm of the residual stream (reference python_vm.py:50-56): fp32
+// statistics; the normalised value is rounded to bf16 and then multiplied by the
+// bf16 weight with a second rounding.  Thread `ctid` normalises elements
+// [c*2048 + ctid*8, +8) of chunk c; the result goes through shared memory to be
+// re-read in the operand layout above.
 template <int NCH>
 __device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, uint32_t &toggle, const bf16 *base,
-                                            bool merge, const bf16 *norm_w, float (&x)[NCH][8]) {
+                                            bool merge, const bf16 *norm_w, uint4 (&x)[NCH][8]) {
     const int lane = ctid & 31, cw = ctid >> 5;
     uint4 wraw[NCH];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) wraw[c] = __ldg(reinterpret_cast<const uint4 *>(norm_w + c * kChunkCols + ctid * 8));
+    float h[NCH][8];
     float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
-        load_hidden8(p, base, merge, c * kChunkCols + ctid * 8, x[c]);
+        load_hidden8(p, base, merge, c * kChunkCols + ctid * 8, h[c]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(x[c][i], x[c][i], ss);
+        for (int i = 0; i < 8; ++i) ss = fmaf(h[c][i], h[c][i], ss);
     }
 #pragma unroll
     for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
@@ -496,47 +437,82 @@ __device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, 
     const float rstd = 1.0f / sqrtf(total / (float)p.hidden + p.eps);
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
-        float w[8];
+        float w[8], y[8];
         unpack8(wraw[c], w);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) x[c][i] = round_bf16(w[i] * round_bf16(x[c][i] * rstd));
+        for (int i = 0; i < 8; ++i) y[i] = round_bf16(w[i] * round_bf16(h[c][i] * rstd));
+        const uint4 packed = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
+                                        pack_bf16x2(y[6], y[7]));
+        *reinterpret_cast<uint4 *>(&s.xbuf[c * kChunkCols + ctid * 8]) = packed;
     }
+    // xbuf is rewritten only after the statistics barrier of the next call,
+    // which no thread reaches before it has finished the reads below.
+    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
+    const int t = lane & 3;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[c][j] = lds128(&s.xbuf[c * kChunkCols + cw * 256 + j * 32 + t * 8]);
 }
 
 template <int NCH>
-__device__ __forceinline__ void load_plain(const bf16 *vec, int ctid, float (&x)[NCH][8]) {
+__device__ __forceinline__ void load_plain(const bf16 *vec, int ctid, uint4 (&x)[NCH][8]) {
+    const int cw = ctid >> 5, t = ctid & 3;
 #pragma unroll
-    for (int c = 0; c < NCH; ++c) ldcg8(vec + c * kChunkCols + ctid * 8, x[c]);
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            x[c][j] = __ldcg(reinterpret_cast<const uint4 *>(vec + c * kChunkCols + cw * 256 + j * 32 + t * 8));
+}
+
+// D += A(16x16, bf16) * B(16x8, bf16), fp32 accumulate, on the tensor cores.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    // volatile: keeps the hand-written load/MMA interleaving (two loads in flight per MMA pair)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // One 16-row block: NCH tiles from the ring times the register-resident
-// activation slice, reduced over the warp and handed to the storer.
+// activation operand.  Lane (g, t) feeds rows g and g+8 of the tile straight
+// from shared memory as MMA A-fragments: its 16-byte load at column offset
+// j*32 + t*8 supplies the k-slots {2t, 2t+1, 2t+8, 2t+9} of two MMAs, and the
+// activation operand uses the same column-to-slot assignment, so no shuffle or
+// conversion is needed.  The per-warp results (16 rows) go to the storer.
 template <int NCH>
 __device__ __forceinline__ void consume_block(const Params &p, Smem &s, ConsumerState &st, int lane, int cw,
-                                              const float (&x)[NCH][8], int opcode, int slot) {
-    float acc[kBlockRows];
-#pragma unroll
-    for (int r = 0; r < kBlockRows; ++r) acc[r] = 0.f;
-    const int col_bytes = (cw * 256 + lane * 8) * 2;
+                                              const uint4 (&x)[NCH][8], int opcode, int slot) {
+    float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
+    const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
+        wait_mbar(p, s, &s.full[st.ring.stage], st.ring.phase, kFailRing, opcode, slot, (int)st.ring.stage);
+        const uint8_t *row_g = s.stage[st.ring.stage] + g * kRowPitch + cw * 512 + t * 16;
+        const uint8_t *row_h = row_g + 8 * kRowPitch;
+        uint4 wg = lds128(row_g), wh = lds128(row_h);
+        uint4 wg1 = lds128(row_g + 64), wh1 = lds128(row_h + 64);
 #pragma unroll
-        for (int sub = 0; sub < kStagesPerTile; ++sub) {
-            wait_mbar(p, s, &s.full[st.ring.stage], st.ring.phase, kFailRing, opcode, slot, (int)st.ring.stage);
-            const uint8_t *base = s.stage[st.ring.stage] + col_bytes;
-            uint4 w[kStageRows];
-#pragma unroll
-            for (int r = 0; r < kStageRows; ++r) w[r] = lds128(base + r * kChunkCols * 2);
-#pragma unroll
-            for (int r = 0; r < kStageRows; ++r) acc[sub * kStageRows + r] = dot8(w[r], x[c], acc[sub * kStageRows + r]);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.empty[st.ring.stage]);
-            st.ring.advance();
+        for (int j = 0; j < 8; ++j) {
+            uint4 wg2 = wg1, wh2 = wh1;
+            if (j + 2 < 8) {  // two column groups of loads stay ahead of the MMAs
+                wg2 = lds128(row_g + (j + 2) * 64);
+                wh2 = lds128(row_h + (j + 2) * 64);
+            }
+            mma_bf16_16816(acc_a, wg.x, wh.x, wg.y, wh.y, x[c][j].x, x[c][j].y);
+            mma_bf16_16816(acc_b, wg.z, wh.z, wg.w, wh.w, x[c][j].z, x[c][j].w);
+            wg = wg1; wh = wh1;
+            wg1 = wg2; wh1 = wh2;
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.empty[st.ring.stage]);
+        st.ring.advance();
     }
-    const float total = warp_reduce16(acc, lane);
     wait_mbar(p, s, &s.pempty[st.pbuf], st.pphase ^ 1u, kFailPartial, opcode, slot, (int)st.pbuf);
-    if ((lane & 1) == 0) s.partial[st.pbuf][cw][lane >> 1] = total;
+    if (t == 0) {  // output column 0
+        s.partial[st.pbuf][cw][g] = acc_a[0] + acc_b[0];
+        s.partial[st.pbuf][cw][g + 8] = acc_a[2] + acc_b[2];
+    }
     __syncwarp();
     if (lane == 0) mbar_arrive(&s.pfull[st.pbuf]);
     st.advance_partial();
@@ -783,7 +759,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
         const int op = __ldg(ins);
         if (op == 0) continue;
         if (ctid == 0) stamp(p, slot, kEvConsumerStart, t_start);
-        float x[NCH][8];
+        uint4 x[NCH][8];
         switch (op) {
         case 1: {
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
@@ -833,7 +809,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             // only the gate/up rows of this 2048-column slice have to be ready
             consumer_wait(p, s, ctid, counter(p, layer, kSliceCounterRow, red), kChunkCols / kBlockRows, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-            float xs[1][8];
+            uint4 xs[1][8];
             load_plain<1>(p.silu_out + (size_t)red * kChunkCols, ctid, xs);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
             for (int b = b0; b < b1; ++b) consume_block<1>(p, s, st, lane, cw, xs, op, slot);
@@ -1236,8 +1212,6 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.skip_attn_reduction = d->skip_attn_reduction;
     p.attn_scale = d->attn_scale; p.eps = d->rms_norm_eps;
     p.spin_cycles = 4000000000ll;
-    p.prefetch_stages = 0;  // measured slower than the ring alone on B200; kept as an option
-    p.prefetch_interval = 700;
     p.down_slices = slices;
     p.down_total = (H / kBlockRows) * slices;
     p.qkv_w = (const bf16 *)d->qkv_w; p.attn_norm_w = (const bf16 *)d->attn_norm_w; p.o_w = (const bf16 *)d->o_w;
@@ -1359,14 +1333,6 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     case MK_OPT_WAIT_BUDGET_CYCLES:
         if (value <= 0) return fail(MK_ERR_BAD_ARGUMENT, "wait budget must be positive");
         h->params.spin_cycles = value;
-        return 0;
-    case MK_OPT_PREFETCH_STAGES:
-        if (value < 0 || value > 256) return fail(MK_ERR_BAD_ARGUMENT, "prefetch distance must be 0..256 stages");
-        h->params.prefetch_stages = (int)value;
-        return 0;
-    case MK_OPT_PREFETCH_INTERVAL:
-        if (value < 0) return fail(MK_ERR_BAD_ARGUMENT, "prefetch interval must not be negative");
-        h->params.prefetch_interval = value;
         return 0;
     default:
         return fail(MK_ERR_BAD_ARGUMENT, "mk_set_option: unknown option %d", option);

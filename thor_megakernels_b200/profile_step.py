@@ -1,0 +1,53 @@
+"""Runs a few decode steps of the benchmark model and nothing else, so that a
+profiler sees only megakernel launches:
+
+    ncu --set full --clock-control none -k regex:decode_step -s 3 -c 1 \\
+        python -m thor_megakernels_b200.profile_step --steps 4
+
+Same model, schedule and cache contents as ``bench.py`` (Llama-3.2-1B
+architecture, bf16, 16-token context); ``--layers`` shrinks the model for a
+smaller capture.  Prints the mean step time measured with CUDA events.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def main():
+    import torch
+
+    import bench
+    from thor_megakernels_b200.runtime import (MK_STEP_EMBED, MK_STEP_RESET_BARRIERS, MK_STEP_WRITE_TOKEN, Megakernel)
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--pos", type=int, default=60)
+    ap.add_argument("--layers", type=int, default=None)
+    args = ap.parse_args()
+    if args.layers is not None:
+        bench.MODEL.update(num_hidden_layers=args.layers)
+    model, sched = bench.build_gpu_model(torch.device("cuda:0"))
+    mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data)
+    tok = torch.tensor([17], dtype=torch.int32, device="cuda")
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    mk.step(args.pos, flags=flags, token_in=tok, token_out=out)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(args.steps):
+        mk.step(args.pos, flags=flags, token_in=tok, token_out=out)
+    end.record()
+    torch.cuda.synchronize()
+    mk.status()
+    print(f"{args.steps} steps at position {args.pos}: {start.elapsed_time(end) / args.steps:.4f} ms/step, token {int(out)}")
+
+
+if __name__ == "__main__":
+    main()
