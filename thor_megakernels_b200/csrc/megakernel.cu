@@ -520,9 +520,14 @@ __device__ __forceinline__ void consume_block(const Params &p, Smem &s, Consumer
 
 // Decode attention of one KV head's 4 query heads over cache rows
 // [t0, t1) (reference python_vm.py:277-346): fp32 scores, softmax and
-// weighted sum; bf16 only at the final store.  Each group of D/8 lanes owns one
-// cache row per iteration, 8 head dimensions per lane.
+// weighted sum; bf16 only at the final store.  A warp takes one cache row per
+// iteration; lane (h = lane/8, sub = lane%8) owns query head h and DPL head
+// dimensions, so a row's dot products need three shuffles and the running
+// softmax state of a head lives in one place per warp.
+template <int DPL>
 __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int *ins, int slot, long long t_start) {
+    constexpr int V = DPL / 8;   // 16-byte vectors per row per lane
+    constexpr int kDepth = DPL == 8 ? 4 : 2;  // rows in flight per lane (register budget)
     const int lane = ctid & 31, cw = ctid >> 5;
     const int layer = __ldg(ins + 1), kv_head = __ldg(ins + 2), num_partials = __ldg(ins + 3), part = __ldg(ins + 4);
     const int D = p.hd;
@@ -538,28 +543,31 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
     int t1 = end_block * 16;
     if (t1 > seq_len) t1 = seq_len;
 
-    const int lanes_per_tok = D / 8;                 // 8 (D=64) or 16 (D=128)
-    const int toks_per_warp = 32 / lanes_per_tok;    // 4 or 2
-    const int sub = lane % lanes_per_tok;
-    const int tslot = lane / lanes_per_tok;
-    const int d0 = sub * 8;
+    const int h = lane >> 3, sub = lane & 7;
+    const int d0 = sub * DPL;
     const size_t tok_stride = (size_t)p.hkv * D;
     const size_t layer_off = (size_t)layer * p.kv_batch * p.kv_len * tok_stride + (size_t)kv_head * D + d0;
     const bf16 *kbase = p.k_cache + layer_off;
     const bf16 *vbase = p.v_cache + layer_off;
-    const int stride_toks = kConsumerWarps * toks_per_warp;
-    const int my_first = t0 + cw * toks_per_warp + tslot;
+    const int my_first = t0 + cw;
+
+    auto load_row = [&](uint4 (&kq)[V], uint4 (&vq)[V], int t) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            kq[v] = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)t * tok_stride) + v);
+            vq[v] = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)t * tok_stride) + v);
+        }
+    };
 
     // Rows below the current position were written by earlier launches: fetch the
-    // first two iterations' worth while the Q/K/V producers are still running.
-    uint4 k_now = make_uint4(0u, 0u, 0u, 0u), v_now = k_now, k_next = k_now, v_next = k_now;
-    if (my_first < t1 && my_first < p.pos) {
-        k_now = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)my_first * tok_stride));
-        v_now = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)my_first * tok_stride));
-    }
-    if (my_first + stride_toks < t1 && my_first + stride_toks < p.pos) {
-        k_next = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)(my_first + stride_toks) * tok_stride));
-        v_next = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)(my_first + stride_toks) * tok_stride));
+    // first kDepth iterations' worth while the Q/K/V producers are still running.
+    uint4 kq[kDepth][V], vq[kDepth][V];
+#pragma unroll
+    for (int j = 0; j < kDepth; ++j) {
+        const int t = my_first + j * kConsumerWarps;
+#pragma unroll
+        for (int v = 0; v < V; ++v) kq[j][v] = vq[j][v] = make_uint4(0u, 0u, 0u, 0u);
+        if (t < t1 && t < p.pos) load_row(kq[j], vq[j], t);
     }
 
     if (ctid == 0) {
@@ -572,95 +580,70 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
     }
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
 
-    uint4 q[kGroup];  // kept packed (bf16 pairs) to save registers
+    uint4 q[V];
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h)
-        q[h] = __ldcg(reinterpret_cast<const uint4 *>(p.q_post + (size_t)(kv_head * kGroup + h) * D + d0));
-    // the row appended by this launch, if it is one of the two fetched early
-    if (my_first < t1 && my_first >= p.pos) {
-        k_now = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)my_first * tok_stride));
-        v_now = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)my_first * tok_stride));
-    }
-    if (my_first + stride_toks < t1 && my_first + stride_toks >= p.pos) {
-        k_next = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)(my_first + stride_toks) * tok_stride));
-        v_next = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)(my_first + stride_toks) * tok_stride));
+    for (int v = 0; v < V; ++v)
+        q[v] = __ldcg(reinterpret_cast<const uint4 *>(p.q_post + (size_t)(kv_head * kGroup + h) * D + d0) + v);
+    // the row appended by this launch, if it is one of those fetched early
+#pragma unroll
+    for (int j = 0; j < kDepth; ++j) {
+        const int t = my_first + j * kConsumerWarps;
+        if (t < t1 && t >= p.pos) load_row(kq[j], vq[j], t);
     }
 
-    float m[kGroup], l[kGroup], acc[kGroup][8];
+    float m = -INFINITY, l = 0.f, acc[DPL];
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-        m[h] = -INFINITY;
-        l[h] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
-    }
-    const float scale_log2e = p.attn_scale * 1.4426950408889634f;  // softmax in base 2; m[] is in log2 units
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    const float scale_log2e = p.attn_scale * 1.4426950408889634f;  // softmax in base 2; m is in log2 units
+    if (ctid == 0) stamp(p, slot, 55, t_start);  // loop entry (loads issued, not yet consumed)
 
+    const int n_iter = (t1 - t0 + kConsumerWarps - 1) / kConsumerWarps;  // same for every warp
 #pragma unroll 1
-    for (int tb = t0; tb < t1; tb += stride_toks) {  // warp-uniform trip count
-        const int t = tb + cw * toks_per_warp + tslot;
-        const uint4 kraw = k_now, vraw = v_now;
-        k_now = k_next;
-        v_now = v_next;
-        const int t2 = t + 2 * stride_toks;  // two iterations of loads stay in flight
-        if (t2 < t1) {
-            k_next = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)t2 * tok_stride));
-            v_next = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)t2 * tok_stride));
-        }
-        float kf[8], vf[8];
-        unpack8(kraw, kf);
-        unpack8(vraw, vf);
-        float sc[kGroup];
+    for (int base = 0; base < n_iter; base += kDepth) {
 #pragma unroll
-        for (int h = 0; h < kGroup; ++h) {
-            float d = dot8(q[h], kf, 0.f);
-            for (int off = 1; off < lanes_per_tok; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-            sc[h] = d * scale_log2e;
-        }
-        if (t < t1) {
+        for (int j = 0; j < kDepth; ++j) {
+            if (base + j < n_iter) {
+                const int t = my_first + (base + j) * kConsumerWarps;
+                float d = 0.f;
+                float vf[DPL];
 #pragma unroll
-            for (int h = 0; h < kGroup; ++h) {
-                const float mn = fmaxf(m[h], sc[h]);
-                const float corr = exp2f(m[h] - mn);  // exp2(-inf) = 0 on the first row
-                const float pr = exp2f(sc[h] - mn);
-                l[h] = l[h] * corr + pr;
+                for (int v = 0; v < V; ++v) {
+                    float kf[8];
+                    unpack8(kq[j][v], kf);
+                    d = dot8(q[v], kf, d);
+                    float tmp[8];
+                    unpack8(vq[j][v], tmp);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(pr, vf[i], acc[h][i] * corr);
-                m[h] = mn;
+                    for (int i = 0; i < 8; ++i) vf[8 * v + i] = tmp[i];
+                }
+                const int t_next = t + kDepth * kConsumerWarps;
+                if (t_next < t1) load_row(kq[j], vq[j], t_next);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                if (t < t1) {
+                    const float sc = d * scale_log2e;
+                    const float mn = fmaxf(m, sc);
+                    const float corr = exp2f(m - mn);  // exp2(-inf) = 0 on the first row
+                    const float pr = exp2f(sc - mn);
+                    l = l * corr + pr;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pr, vf[i], acc[i] * corr);
+                    m = mn;
+                }
             }
         }
     }
+    if (ctid == 0) stamp(p, slot, 56, t_start);  // cache rows consumed
 
-    // merge the token slots of this warp (lanes that differ in the tslot bits)
-    for (int off = lanes_per_tok; off < 32; off <<= 1) {
 #pragma unroll
-        for (int h = 0; h < kGroup; ++h) {
-            const float mo = __shfl_xor_sync(0xffffffffu, m[h], off);
-            const float lo = __shfl_xor_sync(0xffffffffu, l[h], off);
-            const float mn = fmaxf(m[h], mo);
-            const float ca = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - mn);
-            const float cb = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
-            l[h] = l[h] * ca + lo * cb;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float ao = __shfl_xor_sync(0xffffffffu, acc[h][i], off);
-                acc[h][i] = acc[h][i] * ca + ao * cb;
-            }
-            m[h] = mn;
-        }
-    }
-    if (tslot == 0) {
-#pragma unroll
-        for (int h = 0; h < kGroup; ++h) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) s.attn[cw][h][d0 + i] = acc[h][i];
-            if (sub == 0) {
-                s.attn[cw][h][kMaxHeadDim] = m[h];
-                s.attn[cw][h][kMaxHeadDim + 1] = l[h];
-            }
-        }
+    for (int i = 0; i < DPL; ++i) s.attn[cw][h][d0 + i] = acc[i];
+    if (sub == 0) {
+        s.attn[cw][h][kMaxHeadDim] = m;
+        s.attn[cw][h][kMaxHeadDim + 1] = l;
     }
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
+    if (ctid == 0) stamp(p, slot, 57, t_start);  // per-warp states exchanged
 
     // merge the 8 warps; one (head, dim) output per thread iteration
     for (int idx = ctid; idx < kGroup * D; idx += kConsumerThreads) {
@@ -690,6 +673,7 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
         }
     }
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);  // all stores issued; s.attn reusable
+    if (ctid == 0) stamp(p, slot, 58, t_start);  // outputs stored
     if (ctid == 0 && !aborted(s)) {
         if (p.skip_attn_reduction) {
             red_release_gpu_add(counter(p, layer, 2, 0), kGroup);
@@ -775,7 +759,8 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             break;
         }
         case 2:
-            attention_partial(p, s, ctid, ins, slot, t_start);
+            if (p.hd == 64) attention_partial<8>(p, s, ctid, ins, slot, t_start);
+            else attention_partial<16>(p, s, ctid, ins, slot, t_start);
             break;
         case 3:
             attention_reduction(p, s, ctid, ins, slot, t_start);
@@ -893,15 +878,25 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // (reference python_vm.py:196-248, llama.py:136-174)
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
             const size_t cache_row = (((size_t)layer * p.kv_batch) * p.kv_len + p.pos) * (size_t)(p.hkv * D);
+            // rotary factors depend only on the position: fetch those of the first
+            // two blocks before the sums arrive
+            float pre_c[2], pre_s[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int d = ((b0 + i) * kBlockRows + (lane & 15)) % D;
+                pre_c[i] = __ldg(p.rope_cos + (size_t)p.pos * D + d);
+                pre_s[i] = __ldg(p.rope_sin + (size_t)p.pos * D + d);
+            }
             for (int b = b0; b < b1; ++b) {
                 const float y = round_bf16(collect_block(p, s, st, lane, op, slot));
+                if (lane == 0 && b == b0) stamp(p, slot, kEvFirstStore, t_start);
                 const int row = b * kBlockRows + (lane & 15);
                 const float other = __shfl_xor_sync(0xffffffffu, y, 1);
                 float out = y;
                 if (row < v_start) {
                     const int d = row % D;
-                    const float c = __ldg(p.rope_cos + (size_t)p.pos * D + d);
-                    const float sn = __ldg(p.rope_sin + (size_t)p.pos * D + d);
+                    const float c = (b - b0 < 2) ? pre_c[b - b0] : __ldg(p.rope_cos + (size_t)p.pos * D + d);
+                    const float sn = (b - b0 < 2) ? pre_s[b - b0] : __ldg(p.rope_sin + (size_t)p.pos * D + d);
                     const float rot = (lane & 1) ? other : -other;
                     out = __fadd_rn(__fmul_rn(y, c), __fmul_rn(rot, sn));
                 }
@@ -915,6 +910,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // one counter per head; the first release also covers the later heads' rows
             const int bph = D / kBlockRows;
             __syncwarp();
+            if (lane == 0) stamp(p, slot, 59, t_start);  // outputs issued, before the fence
             if (lane == 0 && !aborted(s)) {
                 fence_acq_rel_gpu();  // once; the adds below are relaxed
                 for (int head = b0 / bph; head <= (b1 - 1) / bph; ++head) {
@@ -928,14 +924,24 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // hidden[rows] = bf16(hidden[rows] + bf16(matvec)) (reference python_vm.py:59-104)
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
             const bf16 *base = (layer == 0 && token_row) ? token_row : p.hidden_states;
+            auto residual = [&](int row) {
+                float h = ldcg_bf16(base + row);
+                if (layer > 0)
+                    for (int sl = 0; sl < p.down_slices; ++sl)
+                        h = round_bf16(h + ldcg_bf16(p.down_partials + (size_t)sl * p.hidden + row));
+                return h;
+            };
+            // The residual rows were finished by the previous layer.  If its last
+            // counter already shows that, fetch the first block's rows now instead
+            // of after the sums arrive (this warp is idle until then).
+            const bool early = layer == 0 || ld_acquire_gpu(counter(p, layer - 1, 5, 0)) >= p.down_total;
+            float h_first = 0.f;
+            if (early && lane < kBlockRows) h_first = residual(b0 * kBlockRows + lane);
             for (int b = b0; b < b1; ++b) {
                 const float y = round_bf16(collect_block(p, s, st, lane, op, slot));
                 if (lane < kBlockRows && !aborted(s)) {
                     const int row = b * kBlockRows + lane;
-                    float h = ldcg_bf16(base + row);
-                    if (layer > 0)
-                        for (int sl = 0; sl < p.down_slices; ++sl)
-                            h = round_bf16(h + ldcg_bf16(p.down_partials + (size_t)sl * p.hidden + row));
+                    const float h = (early && b == b0) ? h_first : residual(row);
                     p.hidden_states[row] = __float2bfloat16_rn(h + y);
                 }
             }
@@ -958,6 +964,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // instruction reads), then the reference interpreter's single counter
             const int my_slice = lane < n ? (__ldg(ins + 3 + lane) * kBlockRows) / kChunkCols : -1;
             __syncwarp();
+            if (lane == 0) stamp(p, slot, 59, t_start);  // outputs issued, before the fence
             if (lane == 0) fence_acq_rel_gpu();  // once; the adds below are relaxed
             for (int sl = 0; sl < p.down_slices; ++sl) {
                 const int cnt = __popc(__ballot_sync(0xffffffffu, my_slice == sl));
