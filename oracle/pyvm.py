@@ -63,8 +63,11 @@ def o_proj_residual(g: Globals, ins: O_ProjResidual):
     """latency/python_vm.py:83-104."""
     assert g.barriers[ins.layer_idx, ins.prev_opcode() - 1, 0] == g.num_attention_heads
     assert ins.start_block_idx == ins.end_block_idx - 1 and ins.reduction_block_idx == 0
+    # the reference passes matvec_reduction_size (2048), which is the whole input
+    # width for the only model it supports; wider models reduce over all of it
     matvec_with_residual(g.o_proj_weights[ins.layer_idx], g.attn_out, g.hidden_states, g.o_proj_block_size,
-                         ins.start_block_idx, ins.end_block_idx, g.matvec_reduction_size, ins.reduction_block_idx)
+                         ins.start_block_idx, ins.end_block_idx, g.num_attention_heads * g.head_dim,
+                         ins.reduction_block_idx)
     g.barriers[ins.layer_idx, ins.opcode() - 1, 0] += ins.end_block_idx - ins.start_block_idx
 
 

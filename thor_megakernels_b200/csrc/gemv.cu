@@ -1,0 +1,190 @@
+// Batch 1..8 GEMV  y[b, m] = W[m, k] . x[b, k]  for bf16 or NVFP4 weights
+// (config-1 operator; reference tools/analysis/nvfp4/primitive.cu:79-96 and
+// experimental/weight_only_fp4/primitive.cu:22-70).
+//
+// Work unit = 16 output rows x one 2048-column chunk of K, one CTA of 8 warps
+// per unit, warp w owning columns [w*256, +256) of the chunk.  Weights go from
+// global memory straight into tensor-core A fragments (mma.sync m16n8k16, fp32
+// accumulate); the up-to-8 activation vectors are the 8 columns of the B
+// operand, so batch 2..8 costs no extra weight traffic or instructions.
+//
+//   bf16 weights : lane (g,t) loads 16 bytes of rows g and g+8 per column
+//                  group; bf16 MMA against bf16 activations.
+//   NVFP4 weights: lane (g,t) loads 32 code bytes and 4 scale bytes per row;
+//                  codes -> f16x2 (hardware cvt), times the block scale in f16
+//                  (exact: <= 6 significant bits), f16 MMA against activations
+//                  converted to f16; the fp32 tensor scale is applied to the sum.
+//
+// K > 2048 is split across CTAs: each writes fp32 partial sums to scratch and the
+// last CTA of a row block (atomic ticket) adds them in chunk order, so results
+// do not depend on scheduling.
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/b200_megakernel.h"
+#include "mk_device.cuh"
+#include "fp4_mma.cuh"
+
+namespace mk {
+
+constexpr int kGemvRows = 16;
+constexpr int kGemvChunk = 2048;
+constexpr int kGemvWarps = 8;
+constexpr int kGemvMaxBatch = 8;
+
+template <bool PACKED>
+__global__ void __launch_bounds__(kGemvWarps * 32) gemv_mma_kernel(
+    const bf16 *__restrict__ w, const uint8_t *__restrict__ packed, const uint8_t *__restrict__ scales,
+    const bf16 *__restrict__ x, bf16 *__restrict__ y, int m, int k, float ts, int batch, int chunks,
+    float *__restrict__ partial, int *__restrict__ tickets) {
+    __shared__ float red[kGemvWarps][kGemvRows][kGemvMaxBatch];
+    __shared__ int is_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int row_block = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+    const int col0 = chunk * kGemvChunk + warp * 256;  // this warp's first column
+    const bool active = col0 < k;                      // k is a multiple of 256
+    int row_g = row_block * kGemvRows + g, row_h = row_g + 8;
+    if (row_g >= m) row_g = m - 1;                     // ragged last block: compute on a valid row, never store it
+    if (row_h >= m) row_h = m - 1;
+    const int xcol = g < batch ? g : batch - 1;        // B-operand column g; extra columns repeat the last vector
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) {
+        if constexpr (PACKED) {
+            uint4 cg[2], ch[2];
+            const uint4 *pg = reinterpret_cast<const uint4 *>(packed + ((size_t)row_g * k + col0) / 2 + t * 32);
+            const uint4 *ph = reinterpret_cast<const uint4 *>(packed + ((size_t)row_h * k + col0) / 2 + t * 32);
+            cg[0] = __ldg(pg); cg[1] = __ldg(pg + 1);
+            ch[0] = __ldg(ph); ch[1] = __ldg(ph + 1);
+            const uint32_t sg = __ldg(reinterpret_cast<const uint32_t *>(scales + ((size_t)row_g * k + col0) / 16 + t * 4));
+            const uint32_t sh = __ldg(reinterpret_cast<const uint32_t *>(scales + ((size_t)row_h * k + col0) / 16 + t * 4));
+            uint32_t xh[32];
+            const uint4 *xs = reinterpret_cast<const uint4 *>(x + (size_t)xcol * k + col0 + t * 64);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 v = __ldg(xs + i);
+                xh[4 * i] = bf16x2_to_f16x2(v.x); xh[4 * i + 1] = bf16x2_to_f16x2(v.y);
+                xh[4 * i + 2] = bf16x2_to_f16x2(v.z); xh[4 * i + 3] = bf16x2_to_f16x2(v.w);
+            }
+            fp4_rows_mma(acc, cg, ch, sg, sh, xh);
+        } else {
+            const bf16 *wg = w + (size_t)row_g * k + col0 + t * 8;
+            const bf16 *wh = w + (size_t)row_h * k + col0 + t * 8;
+            const bf16 *xs = x + (size_t)xcol * k + col0 + t * 8;
+            uint4 a[8], b[8], xv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                a[j] = __ldg(reinterpret_cast<const uint4 *>(wg + j * 32));
+                b[j] = __ldg(reinterpret_cast<const uint4 *>(wh + j * 32));
+                xv[j] = __ldg(reinterpret_cast<const uint4 *>(xs + j * 32));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                mma_bf16_16816(acc, a[j].x, b[j].x, a[j].y, b[j].y, xv[j].x, xv[j].y);
+                mma_bf16_16816(acc, a[j].z, b[j].z, a[j].w, b[j].w, xv[j].z, xv[j].w);
+            }
+        }
+    }
+    // C fragment: rows g / g+8, activation columns 2t and 2t+1
+    red[warp][g][2 * t] = acc[0];
+    red[warp][g][2 * t + 1] = acc[1];
+    red[warp][g + 8][2 * t] = acc[2];
+    red[warp][g + 8][2 * t + 1] = acc[3];
+    __syncthreads();
+
+    const int r = threadIdx.x >> 3, c = threadIdx.x & 7;  // 128 threads: one (row, column) each
+    float sum = 0.f;
+    const bool owner = threadIdx.x < kGemvRows * kGemvMaxBatch;
+    if (owner) {
+#pragma unroll
+        for (int wv = 0; wv < kGemvWarps; ++wv) sum += red[wv][r][c];
+    }
+    const int row = row_block * kGemvRows + r;
+    if (chunks == 1) {
+        if (owner && c < batch && row < m) y[(size_t)c * m + row] = __float2bfloat16_rn(sum * ts);
+        return;
+    }
+    // split K: park the chunk's sums, the last chunk to arrive adds them in chunk order
+    if (owner && c < batch && row < m) partial[((size_t)chunk * kGemvMaxBatch + c) * m + row] = sum;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&tickets[row_block], 1);
+        is_last = ticket == chunks - 1;
+        if (is_last) tickets[row_block] = 0;  // ready for the next call
+        __threadfence();
+    }
+    __syncthreads();
+    if (is_last && owner && c < batch && row < m) {
+        float total = 0.f;
+        for (int ch = 0; ch < chunks; ++ch) total += __ldcg(&partial[((size_t)ch * kGemvMaxBatch + c) * m + row]);
+        y[(size_t)c * m + row] = __float2bfloat16_rn(total * ts);
+    }
+}
+
+// Scratch of the split-K path, allocated once per device on first use and kept
+// for the life of the process.
+struct GemvScratch {
+    float *partial = nullptr;
+    int *tickets = nullptr;
+    size_t partial_floats = 0;
+    int ticket_count = 0;
+};
+static GemvScratch g_scratch[64];
+
+static cudaError_t gemv_scratch(int device, size_t floats, int tickets, GemvScratch **out) {
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    GemvScratch &sc = g_scratch[device];
+    if (sc.partial_floats < floats) {
+        if (sc.partial) cudaFree(sc.partial);
+        sc.partial = nullptr; sc.partial_floats = 0;
+        cudaError_t e = cudaMalloc(&sc.partial, floats * sizeof(float));
+        if (e != cudaSuccess) return e;
+        sc.partial_floats = floats;
+    }
+    if (sc.ticket_count < tickets) {
+        if (sc.tickets) cudaFree(sc.tickets);
+        sc.tickets = nullptr; sc.ticket_count = 0;
+        cudaError_t e = cudaMalloc(&sc.tickets, tickets * sizeof(int));
+        if (e != cudaSuccess) return e;
+        e = cudaMemset(sc.tickets, 0, tickets * sizeof(int));
+        if (e != cudaSuccess) return e;
+        sc.ticket_count = tickets;
+    }
+    *out = &sc;
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemv_mma(const void *w, const void *packed, const void *scales, const void *x, void *y, int m, int k,
+                            float ts, int is_packed, int batch, cudaStream_t stream) {
+    const int row_blocks = (m + kGemvRows - 1) / kGemvRows;
+    const int chunks = (k + kGemvChunk - 1) / kGemvChunk;
+    float *partial = nullptr;
+    int *tickets = nullptr;
+    if (chunks > 1) {
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return e;
+        GemvScratch *sc = nullptr;
+        e = gemv_scratch(device, (size_t)chunks * kGemvMaxBatch * m, row_blocks, &sc);
+        if (e != cudaSuccess) return e;
+        partial = sc->partial;
+        tickets = sc->tickets;
+    }
+    const dim3 grid(row_blocks * chunks), block(kGemvWarps * 32);
+    if (is_packed)
+        gemv_mma_kernel<true><<<grid, block, 0, stream>>>(nullptr, (const uint8_t *)packed, (const uint8_t *)scales,
+                                                          (const bf16 *)x, (bf16 *)y, m, k, ts, batch, chunks, partial, tickets);
+    else
+        gemv_mma_kernel<false><<<grid, block, 0, stream>>>((const bf16 *)w, nullptr, nullptr, (const bf16 *)x, (bf16 *)y,
+                                                           m, k, 1.0f, batch, chunks, partial, tickets);
+    return cudaGetLastError();
+}
+
+}  // namespace mk

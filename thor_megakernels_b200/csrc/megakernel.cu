@@ -33,6 +33,7 @@
 
 #include "../../include/b200_megakernel.h"
 #include "mk_device.cuh"
+#include "fp4_mma.cuh"
 
 namespace mk {
 
@@ -47,7 +48,21 @@ constexpr int kRowBytes = kChunkCols * 2;                 // 4 KiB of a weight r
 constexpr int kRowPitch = kRowBytes + 64;
 constexpr int kTileBytes = kBlockRows * kRowBytes;        // 64 KiB moved per tile
 constexpr int kStageBytes = kBlockRows * kRowPitch;       // shared-memory footprint of a tile
-constexpr int kStages = 3;                                // tiles in flight per SM (192 KiB)
+constexpr int kStages = 3;                                // bf16 tiles in flight per SM (192 KiB)
+constexpr int kRingBytes = kStages * kStageBytes;
+// NVFP4 tile: 16 rows x 1024 code bytes, then 16 rows x 128 scale bytes
+constexpr int kFp4CodeRow = kChunkCols / 2;
+constexpr int kFp4ScaleRow = kChunkCols / 16;
+constexpr int kFp4ScaleOffset = kBlockRows * kFp4CodeRow;
+constexpr int kFp4TileBytes = kBlockRows * (kFp4CodeRow + kFp4ScaleRow);  // 18 KiB
+constexpr int kFp4Stages = kRingBytes / kFp4TileBytes;                    // 10 tiles in flight
+constexpr int kMaxStages = kFp4Stages > kStages ? kFp4Stages : kStages;
+
+template <bool FP4> struct Fmt {
+    static constexpr int stages = FP4 ? kFp4Stages : kStages;
+    static constexpr int stage_bytes = FP4 ? kFp4TileBytes : kStageBytes;
+    static constexpr int tile_tx = FP4 ? kFp4TileBytes : kTileBytes;  // bytes a fill delivers
+};
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = (1 + kConsumerWarps + 1) * 32;   // loader + consumers + storer
@@ -60,6 +75,7 @@ constexpr int kTimingSlots = 128;
 constexpr int kConsumerBarrier = 1;                       // named barrier id
 constexpr int kSliceCounterRow = 7;                       // barriers[layer, 7, slice]: gate/up blocks done per 2048-column slice
 constexpr int kMaxDownSlices = 8;                         // intermediate_size <= 16384
+constexpr int kTaggedPartials = 32;                       // attention slices per KV head the scratch can hold
 
 // timing slots (reference include/util.cuh:225-256)
 constexpr int kEvLoaderStart = 5, kEvStorerStart = 9, kEvConsumerStart = 11;
@@ -67,7 +83,7 @@ constexpr int kEvAtWait = 44, kEvDoneWait = 45, kEvFirstLoad = 48, kEvFirstUse =
 constexpr int kEvLastLoad = 51, kEvLastUse = 52, kEvLastStore = 53, kEvOutputReady = 54;
 
 // status codes
-constexpr int kFailCounter = 1, kFailRing = 2, kFailPartial = 3, kFailOpcode = 4;
+constexpr int kFailCounter = 1, kFailRing = 2, kFailPartial = 3, kFailOpcode = 4, kFailData = 5;
 
 struct Params {
     // shapes
@@ -86,6 +102,12 @@ struct Params {
     int down_total;   // (hidden / 16) * down_slices
     // weights
     const bf16 *qkv_w, *attn_norm_w, *o_w, *mlp_norm_w, *up_w, *gate_w, *down_w, *lm_norm_w, *lm_w, *embed_w;
+    // NVFP4 weights: per-layer tables in device memory (null for bf16 models)
+    const MkNvfp4Matrix *q_qkv, *q_o, *q_up, *q_gate, *q_down, *q_lm;
+    // 1: every linear output and the SiLU product are rounded once from fp32, the
+    // rounding points of the reference's quantised-model oracle
+    // (tools/analysis/nvfp4/model_reference.py:39-61); 0: the bf16 interpreter's
+    int model_numerics;
     // cache + tables
     bf16 *k_cache, *v_cache;
     const float *rope_cos, *rope_sin;
@@ -98,7 +120,19 @@ struct Params {
     const int *instructions;
     int *timings;
     // handle-owned scratch
-    bf16 *down_partials;            // [down_slices][hidden]
+    // Tagged cells (8 bytes: payload + launch tag), one set per layer so that no
+    // cell is written twice in a launch.  Two bf16 per cell unless noted.
+    unsigned long long *t_resid;    // [L][hidden/2]            residual stream after the attention block
+    unsigned long long *t_hidden;   // [L][hidden/2]            residual stream after the MLP block (layer output)
+    unsigned long long *t_down;     // [L][down_slices][hidden] one fp32 per cell: down-projection slice sums
+    unsigned long long *t_q;        // [L][hq*hd/2]
+    unsigned long long *t_k;        // [L][hkv*hd/2]            this token's key row
+    unsigned long long *t_v;        // [L][hkv*hd/2]
+    unsigned long long *t_attn;     // [L][hq*hd/2]
+    unsigned long long *t_silu;     // [L][inter/2]
+    unsigned long long *t_oi;       // [L][hq][kTaggedPartials][hd] one fp32 per cell: attention partial outputs
+    unsigned long long *t_lse;      // [L][hq][kTaggedPartials]     one fp32 per cell
+    unsigned *epoch;                // launch tag, advanced by the last CTA of every launch
     unsigned long long *argmax_key;
     int *done_counter;
     int *status;                    // [0] code [1] worker [2] opcode [3] slot [4] detail [5] expected [7] abort
@@ -107,13 +141,13 @@ struct Params {
 };
 
 struct __align__(128) Smem {
-    uint8_t stage[kStages][kStageBytes];
+    uint8_t ring[kRingBytes];
     float attn[kConsumerWarps][kGroup][kMaxHeadDim + 2];
     float partial[kPartialBufs][kConsumerWarps][kBlockRows];
     float red[2][kConsumerWarps];
     __align__(16) bf16 xbuf[2 * kChunkCols];  // normalised activations, re-read in the MMA operand layout
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t pfull[kPartialBufs];
     uint64_t pempty[kPartialBufs];
     int abort_flag;
@@ -162,17 +196,19 @@ __device__ __forceinline__ void wait_mbar(const Params &p, Smem &s, uint64_t *ba
     }
 }
 
-// One thread polls a dependency counter until it reaches `expected`.
+// One thread polls a dependency counter until it reaches `expected`.  The
+// counter is only a hint that the producers' cells are (about to be) valid; the
+// data itself is checked cell by cell, so relaxed accesses suffice.
 __device__ __forceinline__ void wait_counter(const Params &p, Smem &s, const int *ctr, int expected, int opcode,
                                              int slot) {
     if (aborted(s)) return;
-    int v = ld_acquire_gpu(ctr);
+    int v = ld_relaxed_gpu(ctr);
     if (v >= expected) return;
     const long long t0 = clock64();
     unsigned it = 0;
     while (true) {
         __nanosleep(20);
-        v = ld_acquire_gpu(ctr);
+        v = ld_relaxed_gpu(ctr);
         if (v >= expected) return;
         if ((++it & 15u) == 0) {
             if (aborted(s)) return;
@@ -186,6 +222,108 @@ __device__ __forceinline__ void wait_counter(const Params &p, Smem &s, const int
             }
         }
     }
+}
+
+// ---------------------------------------------------------------------------
+// validated loads of tagged cells
+// ---------------------------------------------------------------------------
+
+struct Deadline {
+    long long t0;
+    unsigned it;
+};
+__device__ __forceinline__ Deadline start_deadline() { return Deadline{clock64(), 0u}; }
+
+// Called between two attempts to read cells that were not all valid.  Returns
+// false when the caller must give up (abort raised or budget spent).
+__device__ __forceinline__ bool keep_waiting(const Params &p, Smem &s, Deadline &d, int opcode, int slot, int detail) {
+    __nanosleep(40);
+    if ((++d.it & 7u) == 0) {
+        if (aborted(s)) return false;
+        if (ld_relaxed_gpu(&p.status[7]) != 0) {
+            *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+            return false;
+        }
+        if (clock64() - d.t0 > p.spin_cycles) {
+            report_failure(p, s, kFailData, opcode, slot, detail, 0);
+            return false;
+        }
+    }
+    return !aborted(s);
+}
+
+// Eight bf16 values = four cells (32 bytes, 32-byte aligned).
+__device__ __forceinline__ bool try_load8(const unsigned long long *cells, uint32_t tag, uint4 &out) {
+    const ulonglong2 a = ld_tagged2(cells), b = ld_tagged2(cells + 2);
+    out = make_uint4(tag_payload(a.x), tag_payload(a.y), tag_payload(b.x), tag_payload(b.y));
+    return tag_ok(a.x, tag) & tag_ok(a.y, tag) & tag_ok(b.x, tag) & tag_ok(b.y, tag);
+}
+
+// Eight fp32 values = eight cells.
+__device__ __forceinline__ bool try_load8f(const unsigned long long *cells, uint32_t tag, float (&out)[8]) {
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const ulonglong2 a = ld_tagged2(cells + 2 * i);
+        out[2 * i] = __uint_as_float(tag_payload(a.x));
+        out[2 * i + 1] = __uint_as_float(tag_payload(a.y));
+        ok &= tag_ok(a.x, tag) & tag_ok(a.y, tag);
+    }
+    return ok;
+}
+
+struct F8 { float v[8]; };
+
+// Slow paths, kept out of line so that their loops do not inflate the register
+// footprint of the streaming code around the (almost always successful) first try.
+__device__ __noinline__ uint4 load8_slow(const Params &p, Smem &s, const unsigned long long *cells, uint32_t tag,
+                                         int opcode, int slot) {
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    Deadline d = start_deadline();
+    while (keep_waiting(p, s, d, opcode, slot, 0))
+        if (try_load8(cells, tag, out)) break;
+    return out;
+}
+
+__device__ __noinline__ F8 load8f_slow(const Params &p, Smem &s, const unsigned long long *cells, uint32_t tag,
+                                       int opcode, int slot) {
+    F8 out;
+    Deadline d = start_deadline();
+    while (keep_waiting(p, s, d, opcode, slot, 1))
+        if (try_load8f(cells, tag, out.v)) break;
+    return out;
+}
+
+__device__ __noinline__ uint32_t load1_slow(const Params &p, Smem &s, const unsigned long long *cell, uint32_t tag,
+                                            int opcode, int slot) {
+    unsigned long long v = 0;
+    Deadline d = start_deadline();
+    while (keep_waiting(p, s, d, opcode, slot, 2)) {
+        v = ld_tagged1(cell);
+        if (tag_ok(v, tag)) break;
+    }
+    return tag_payload(v);
+}
+
+__device__ __forceinline__ void load8_wait(const Params &p, Smem &s, const unsigned long long *cells, uint32_t tag,
+                                           uint4 &out, int opcode, int slot) {
+    if (try_load8(cells, tag, out) || aborted(s)) return;
+    out = load8_slow(p, s, cells, tag, opcode, slot);
+}
+
+__device__ __forceinline__ void load8f_wait(const Params &p, Smem &s, const unsigned long long *cells, uint32_t tag,
+                                            float (&out)[8], int opcode, int slot) {
+    if (try_load8f(cells, tag, out) || aborted(s)) return;
+    const F8 r = load8f_slow(p, s, cells, tag, opcode, slot);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = r.v[i];
+}
+
+__device__ __forceinline__ uint32_t load1_wait(const Params &p, Smem &s, const unsigned long long *cell, uint32_t tag,
+                                               int opcode, int slot) {
+    const unsigned long long v = ld_tagged1(cell);
+    if (tag_ok(v, tag) || aborted(s)) return tag_payload(v);
+    return load1_slow(p, s, cell, tag, opcode, slot);
 }
 
 __device__ __forceinline__ int *counter(const Params &p, int layer, int row, int col) {
@@ -205,25 +343,29 @@ __device__ __forceinline__ void stamp(const Params &p, int slot, int event, long
 // loader
 // ---------------------------------------------------------------------------
 
+template <int STAGES>
 struct Ring {
     uint32_t stage = 0;
     uint32_t phase = 0;
     __device__ __forceinline__ void advance() {
-        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
     }
 };
 
 // One 16-row x 2048-column weight tile: first byte, row pitch, owning instruction.
+// NVFP4: `src` are the codes (two per byte), `scales` the block scales.
 struct Tile {
     const uint8_t *src;
     size_t stride_bytes;
+    const uint8_t *scales;
+    size_t scale_stride;
     int opcode;
     int slot;
 };
 
 // Walks a worker's instruction queue and yields its weight tiles in the order
 // the consumers use them.
-template <int NCH>
+template <int NCH, bool FP4>
 struct TileCursor {
     int slot = -1;
     int op = 0;
@@ -231,17 +373,41 @@ struct TileCursor {
     int sub = 0, nsub = 1;  // tile position within the block
     int first_block = 0;
     const int *ins = nullptr;
-    const bf16 *base = nullptr, *base2 = nullptr;
-    size_t row_elems = 0;
+    // bf16: element pointers; NVFP4: code / scale byte pointers (second pair = gate matrix of op 5)
+    const uint8_t *base = nullptr, *base2 = nullptr, *sbase = nullptr, *sbase2 = nullptr;
+    size_t row_elems = 0;   // K of the matrix
+    size_t col0 = 0;        // first column (down projection: the instruction's 2048-column slice)
+
+    __device__ __forceinline__ void bind(const bf16 *w, const MkNvfp4Matrix *q, size_t layer, size_t layer_elems,
+                                         bool second) {
+        const uint8_t *b, *sb = nullptr;
+        if constexpr (FP4) {
+            b = q[layer].packed;
+            sb = q[layer].scales;
+        } else {
+            b = reinterpret_cast<const uint8_t *>(w + layer * layer_elems);
+        }
+        if (second) { base2 = b; sbase2 = sb; } else { base = b; sbase = sb; }
+    }
 
     __device__ __forceinline__ bool next(const Params &p, Tile &t) {
         while (true) {
             if (idx < cnt) {
                 const int block = (op == 5) ? __ldg(ins + 3 + idx) : first_block + idx;
-                const bf16 *w = (op == 5 && sub >= NCH) ? base2 : base;
-                const int chunk = (op == 6) ? 0 : (sub % NCH);
-                t.src = reinterpret_cast<const uint8_t *>(w + (size_t)block * kBlockRows * row_elems + chunk * kChunkCols);
-                t.stride_bytes = row_elems * sizeof(bf16);
+                const bool second = op == 5 && sub >= NCH;
+                const size_t col = col0 + (size_t)((op == 6) ? 0 : (sub % NCH)) * kChunkCols;
+                const size_t elem = (size_t)block * kBlockRows * row_elems + col;
+                if constexpr (FP4) {
+                    t.src = (second ? base2 : base) + elem / 2;
+                    t.stride_bytes = row_elems / 2;
+                    t.scales = (second ? sbase2 : sbase) + elem / 16;
+                    t.scale_stride = row_elems / 16;
+                } else {
+                    t.src = (second ? base2 : base) + elem * sizeof(bf16);
+                    t.stride_bytes = row_elems * sizeof(bf16);
+                    t.scales = nullptr;
+                    t.scale_stride = 0;
+                }
                 t.opcode = op;
                 t.slot = slot;
                 if (++sub == nsub) { sub = 0; ++idx; }
@@ -250,40 +416,43 @@ struct TileCursor {
             if (++slot >= p.queue_len) return false;
             ins = instruction_at(p, slot);
             op = __ldg(ins);
-            idx = 0; sub = 0; cnt = 0; nsub = NCH;
+            idx = 0; sub = 0; cnt = 0; nsub = NCH; col0 = 0;
             const size_t hidden = p.hidden;
             switch (op) {
             case 1: {
                 const int layer = __ldg(ins + 1);
                 first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block;
-                base = p.qkv_w + (size_t)layer * p.qkv_rows * hidden; row_elems = hidden;
+                row_elems = hidden;
+                bind(p.qkv_w, p.q_qkv, layer, (size_t)p.qkv_rows * hidden, false);
                 break;
             }
             case 4: {
                 const int layer = __ldg(ins + 1);
                 first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block;
                 row_elems = (size_t)p.hq * p.hd;
-                base = p.o_w + (size_t)layer * hidden * row_elems;
+                bind(p.o_w, p.q_o, layer, hidden * row_elems, false);
                 break;
             }
             case 5: {
                 const int layer = __ldg(ins + 1);
                 cnt = __ldg(ins + 2); nsub = 2 * NCH;  // up tiles, then gate tiles
-                base = p.up_w + (size_t)layer * p.inter * hidden;
-                base2 = p.gate_w + (size_t)layer * p.inter * hidden;
                 row_elems = hidden;
+                bind(p.up_w, p.q_up, layer, (size_t)p.inter * hidden, false);
+                bind(p.gate_w, p.q_gate, layer, (size_t)p.inter * hidden, true);
                 break;
             }
             case 6: {
                 const int layer = __ldg(ins + 1);
                 first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block; nsub = 1;
                 row_elems = p.inter;
-                base = p.down_w + (size_t)layer * hidden * row_elems + (size_t)__ldg(ins + 4) * kChunkCols;
+                col0 = (size_t)__ldg(ins + 4) * kChunkCols;
+                bind(p.down_w, p.q_down, layer, hidden * row_elems, false);
                 break;
             }
             case 7:
                 first_block = __ldg(ins + 1); cnt = __ldg(ins + 2) - first_block;
-                base = p.lm_w; row_elems = hidden;
+                row_elems = hidden;
+                bind(p.lm_w, p.q_lm, 0, 0, false);
                 break;
             default:
                 break;  // attention ops, no-ops and unknown opcodes stream no weights
@@ -293,12 +462,13 @@ struct TileCursor {
     }
 };
 
-template <int NCH>
+template <int NCH, bool FP4>
 __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
+    using F = Fmt<FP4>;
     const uint64_t policy = l2_evict_first_policy();
-    Ring ring;
+    Ring<F::stages> ring;
     uint32_t live = 0;  // stages whose most recent fill was actually issued
-    TileCursor<NCH> tiles;
+    TileCursor<NCH, FP4> tiles;
     Tile t;
     int last_slot = -1;
     while (tiles.next(p, t)) {
@@ -312,11 +482,27 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
             live &= ~(1u << ring.stage);
         } else {
             live |= 1u << ring.stage;
-            mbar_arrive_expect_tx(&s.full[ring.stage], kTileBytes);
-            uint8_t *dst = s.stage[ring.stage];
+            uint64_t *bar = &s.full[ring.stage];
+            mbar_arrive_expect_tx(bar, F::tile_tx);
+            uint8_t *dst = s.ring + ring.stage * F::stage_bytes;
+            if constexpr (FP4) {
+                // rows of a K=2048 matrix are contiguous: one copy each for codes and scales
+                if (t.stride_bytes == (size_t)kFp4CodeRow) {
+                    bulk_load(dst, t.src, kBlockRows * kFp4CodeRow, bar, policy);
+                    bulk_load(dst + kFp4ScaleOffset, t.scales, kBlockRows * kFp4ScaleRow, bar, policy);
+                } else {
 #pragma unroll 4
-            for (int r = 0; r < kBlockRows; ++r)
-                bulk_load(dst + r * kRowPitch, t.src + r * t.stride_bytes, kRowBytes, &s.full[ring.stage], policy);
+                    for (int r = 0; r < kBlockRows; ++r) {
+                        bulk_load(dst + r * kFp4CodeRow, t.src + r * t.stride_bytes, kFp4CodeRow, bar, policy);
+                        bulk_load(dst + kFp4ScaleOffset + r * kFp4ScaleRow, t.scales + r * t.scale_stride, kFp4ScaleRow,
+                                  bar, policy);
+                    }
+                }
+            } else {
+#pragma unroll 4
+                for (int r = 0; r < kBlockRows; ++r)
+                    bulk_load(dst + r * kRowPitch, t.src + r * t.stride_bytes, kRowBytes, bar, policy);
+            }
         }
         ring.advance();
     }
@@ -325,7 +511,7 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
     // been waited for by the consumers; when aborting, wait here (bounded,
     // ignoring the abort flag) for the last fill of every stage.
     if (aborted(s)) {
-        for (uint32_t st = 0; st < (uint32_t)kStages; ++st) {
+        for (uint32_t st = 0; st < (uint32_t)F::stages; ++st) {
             if (!(live & (1u << st))) continue;
             const uint32_t ph = st < ring.stage ? ring.phase : (ring.phase ^ 1u);
             const long long t0 = clock64();
@@ -340,8 +526,9 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
 // consumer
 // ---------------------------------------------------------------------------
 
+template <bool FP4>
 struct ConsumerState {
-    Ring ring;
+    Ring<Fmt<FP4>::stages> ring;
     uint32_t pbuf = 0;
     uint32_t pphase = 0;
     uint32_t norm_toggle = 0;
@@ -357,37 +544,25 @@ __device__ __forceinline__ void consumer_wait(const Params &p, Smem &s, int ctid
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
 }
 
-// 8 consecutive elements of the residual stream starting at `idx`.  `base` is
-// the stream as last written in place; with `merge` the down-projection's
-// column-slice partial sums of the previous layer are added one slice at a
-// time, each add rounded to bf16, which is the order and rounding of the
-// reference interpreter's sequential `hidden += partial` updates.
-__device__ __forceinline__ void load_hidden8(const Params &p, const bf16 *base, bool merge, int idx, float (&h)[8]) {
-    const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(base + idx));
-    if (!merge) {
-        unpack8(raw, h);
+// fp32 tensor scale of a quantised matrix (1 for bf16 weights)
+__device__ __forceinline__ float matrix_scale(const MkNvfp4Matrix *table, int layer) {
+    return table ? __ldg(&table[layer].tensor_scale) : 1.0f;
+}
+__device__ __forceinline__ float down_scale(const Params &p, int layer) { return matrix_scale(p.q_down, layer); }
+
+// 8 consecutive elements (starting at `idx`, a multiple of 8) of a bf16 vector
+// that is either plain memory written before the launch (`plain`: the step input)
+// or tagged cells written by other SMs during it.
+__device__ __forceinline__ void load_vector8(const Params &p, Smem &s, uint32_t tag, const bf16 *plain,
+                                             const unsigned long long *cells, int idx, float (&h)[8], int opcode,
+                                             int slot) {
+    if (plain != nullptr) {
+        ldcg8(plain + idx, h);
         return;
     }
-    // slices in groups of four: all loads of a group are issued before its dependent adds
-    bool first = true;
-    for (int s0 = 0; s0 < p.down_slices; s0 += 4) {
-        uint4 parts[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (s0 + j < p.down_slices)
-                parts[j] = __ldcg(reinterpret_cast<const uint4 *>(p.down_partials + (size_t)(s0 + j) * p.hidden + idx));
-        if (first) { unpack8(raw, h); first = false; }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (s0 + j < p.down_slices) {
-                float part[8];
-                unpack8(parts[j], part);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) h[i] = round_bf16(h[i] + part[i]);
-            }
-        }
-    }
-    if (first) unpack8(raw, h);
+    uint4 raw;
+    load8_wait(p, s, cells + idx / 2, tag, raw, opcode, slot);
+    unpack8(raw, h);
 }
 
 // Activation operand of the tensor-core matvec.  Consumer warp `cw` owns input
@@ -395,8 +570,20 @@ __device__ __forceinline__ void load_hidden8(const Params &p, const bf16 *base, 
 // (g = lane/4, t = lane%4) holds for j = 0..7 the eight bf16 values of columns
 // cw*256 + j*32 + t*8 .. +7 (one uint4).  All eight g-groups hold the same
 // values: the MMA's eight output columns are copies and only column 0 is kept.
-template <int NCH>
-using XOperand = uint4[NCH][8];
+//
+// NVFP4 weights use a different assignment because a lane's 32 code bytes of a
+// row are contiguous: x[c][j] holds columns cw*256 + t*64 + j*8 .. +7, converted
+// to f16 (the MMA's A operand, code x block scale, is exact in f16).
+template <bool FP4>
+__device__ __forceinline__ int operand_column(int cw, int t, int j) {
+    return FP4 ? cw * 256 + t * 64 + j * 8 : cw * 256 + j * 32 + t * 8;
+}
+
+template <bool FP4>
+__device__ __forceinline__ uint4 operand_convert(uint4 v) {
+    if constexpr (FP4) return make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+    else return v;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     // both inputs already hold bf16-representable values
@@ -408,9 +595,10 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // bf16 weight with a second rounding.  Thread `ctid` normalises elements
 // [c*2048 + ctid*8, +8) of chunk c; the result goes through shared memory to be
 // re-read in the operand layout above.
-template <int NCH>
-__device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, uint32_t &toggle, const bf16 *base,
-                                            bool merge, const bf16 *norm_w, uint4 (&x)[NCH][8]) {
+template <int NCH, bool FP4>
+__device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, uint32_t &toggle, uint32_t tag,
+                                            const bf16 *plain, const unsigned long long *cells, const bf16 *norm_w,
+                                            uint4 (&x)[NCH][8], int opcode, int slot) {
     const int lane = ctid & 31, cw = ctid >> 5;
     uint4 wraw[NCH];
 #pragma unroll
@@ -419,7 +607,7 @@ __device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, 
     float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
-        load_hidden8(p, base, merge, c * kChunkCols + ctid * 8, h[c]);
+        load_vector8(p, s, tag, plain, cells, c * kChunkCols + ctid * 8, h[c], opcode, slot);
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss = fmaf(h[c][i], h[c][i], ss);
     }
@@ -452,26 +640,37 @@ __device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, 
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[c][j] = lds128(&s.xbuf[c * kChunkCols + cw * 256 + j * 32 + t * 8]);
+        for (int j = 0; j < 8; ++j)
+            x[c][j] = operand_convert<FP4>(lds128(&s.xbuf[c * kChunkCols + operand_column<FP4>(cw, t, j)]));
 }
 
-template <int NCH>
-__device__ __forceinline__ void load_plain(const bf16 *vec, int ctid, uint4 (&x)[NCH][8]) {
+// Operand from tagged cells (two bf16 per cell) of a vector that starts at
+// `cells`: attention output for the output projection, one 2048-column slice of
+// the SiLU product for the down projection.  Each thread fetches and validates 8
+// elements once; the operand layout (in which the 8 row groups of a warp hold the
+// same values) is then read from shared memory, so L2 sees every element once per
+// SM instead of eight times.  Callers synchronise the consumer warps between the
+// previous reads of xbuf and this call (their dependency wait does).
+template <int NCH, bool FP4>
+__device__ __forceinline__ void load_operand(const Params &p, Smem &s, const unsigned long long *cells, uint32_t tag,
+                                             int ctid, uint4 (&x)[NCH][8], int opcode, int slot) {
     const int cw = ctid >> 5, t = ctid & 3;
+    uint4 mine[NCH];
+    uint32_t missing = 0;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+        if (!try_load8(cells + (c * kChunkCols + ctid * 8) / 2, tag, mine[c])) missing |= 1u << c;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        if (missing & (1u << c)) load8_wait(p, s, cells + (c * kChunkCols + ctid * 8) / 2, tag, mine[c], opcode, slot);
+        *reinterpret_cast<uint4 *>(&s.xbuf[c * kChunkCols + ctid * 8]) = mine[c];
+    }
+    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            x[c][j] = __ldcg(reinterpret_cast<const uint4 *>(vec + c * kChunkCols + cw * 256 + j * 32 + t * 8));
-}
-
-// D += A(16x16, bf16) * B(16x8, bf16), fp32 accumulate, on the tensor cores.
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-    // volatile: keeps the hand-written load/MMA interleaving (two loads in flight per MMA pair)
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+            x[c][j] = operand_convert<FP4>(lds128(&s.xbuf[c * kChunkCols + operand_column<FP4>(cw, t, j)]));
 }
 
 // One 16-row block: NCH tiles from the ring times the register-resident
@@ -480,29 +679,42 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 // j*32 + t*8 supplies the k-slots {2t, 2t+1, 2t+8, 2t+9} of two MMAs, and the
 // activation operand uses the same column-to-slot assignment, so no shuffle or
 // conversion is needed.  The per-warp results (16 rows) go to the storer.
-template <int NCH>
-__device__ __forceinline__ void consume_block(const Params &p, Smem &s, ConsumerState &st, int lane, int cw,
+template <int NCH, bool FP4>
+__device__ __forceinline__ void consume_block(const Params &p, Smem &s, ConsumerState<FP4> &st, int lane, int cw,
                                               const uint4 (&x)[NCH][8], int opcode, int slot) {
     float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
         wait_mbar(p, s, &s.full[st.ring.stage], st.ring.phase, kFailRing, opcode, slot, (int)st.ring.stage);
-        const uint8_t *row_g = s.stage[st.ring.stage] + g * kRowPitch + cw * 512 + t * 16;
-        const uint8_t *row_h = row_g + 8 * kRowPitch;
-        uint4 wg = lds128(row_g), wh = lds128(row_h);
-        uint4 wg1 = lds128(row_g + 64), wh1 = lds128(row_h + 64);
+        const uint8_t *tile = s.ring + st.ring.stage * Fmt<FP4>::stage_bytes;
+        if constexpr (FP4) {
+            // 32 code bytes and 4 scale bytes per row: columns cw*256 + t*64 .. +63
+            const uint8_t *cg = tile + g * kFp4CodeRow + cw * 128 + t * 32;
+            const uint8_t *ch = cg + 8 * kFp4CodeRow;
+            const uint8_t *sg = tile + kFp4ScaleOffset + g * kFp4ScaleRow + cw * 16 + t * 4;
+            const uint4 codes_g[2] = {lds128(cg), lds128(cg + 16)};
+            const uint4 codes_h[2] = {lds128(ch), lds128(ch + 16)};
+            const uint32_t sc_g = *reinterpret_cast<const uint32_t *>(sg);
+            const uint32_t sc_h = *reinterpret_cast<const uint32_t *>(sg + 8 * kFp4ScaleRow);
+            fp4_rows_mma(acc_a, codes_g, codes_h, sc_g, sc_h, x[c]);
+        } else {
+            const uint8_t *row_g = tile + g * kRowPitch + cw * 512 + t * 16;
+            const uint8_t *row_h = row_g + 8 * kRowPitch;
+            uint4 wg = lds128(row_g), wh = lds128(row_h);
+            uint4 wg1 = lds128(row_g + 64), wh1 = lds128(row_h + 64);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            uint4 wg2 = wg1, wh2 = wh1;
-            if (j + 2 < 8) {  // two column groups of loads stay ahead of the MMAs
-                wg2 = lds128(row_g + (j + 2) * 64);
-                wh2 = lds128(row_h + (j + 2) * 64);
+            for (int j = 0; j < 8; ++j) {
+                uint4 wg2 = wg1, wh2 = wh1;
+                if (j + 2 < 8) {  // two column groups of loads stay ahead of the MMAs
+                    wg2 = lds128(row_g + (j + 2) * 64);
+                    wh2 = lds128(row_h + (j + 2) * 64);
+                }
+                mma_bf16_16816(acc_a, wg.x, wh.x, wg.y, wh.y, x[c][j].x, x[c][j].y);
+                mma_bf16_16816(acc_b, wg.z, wh.z, wg.w, wh.w, x[c][j].z, x[c][j].w);
+                wg = wg1; wh = wh1;
+                wg1 = wg2; wh1 = wh2;
             }
-            mma_bf16_16816(acc_a, wg.x, wh.x, wg.y, wh.y, x[c][j].x, x[c][j].y);
-            mma_bf16_16816(acc_b, wg.z, wh.z, wg.w, wh.w, x[c][j].z, x[c][j].w);
-            wg = wg1; wh = wh1;
-            wg1 = wg2; wh1 = wh2;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.empty[st.ring.stage]);
@@ -525,9 +737,10 @@ __device__ __forceinline__ void consume_block(const Params &p, Smem &s, Consumer
 // dimensions, so a row's dot products need three shuffles and the running
 // softmax state of a head lives in one place per warp.
 template <int DPL>
-__device__ void attention_partial(const Params &p, Smem &s, int ctid, const int *ins, int slot, long long t_start) {
+__device__ void attention_partial(const Params &p, Smem &s, int ctid, uint32_t tag, const int *ins, int slot,
+                                  long long t_start) {
     constexpr int V = DPL / 8;   // 16-byte vectors per row per lane
-    constexpr int kDepth = DPL == 8 ? 4 : 2;  // rows in flight per lane (register budget)
+    constexpr int kDepth = DPL == 8 ? 8 : 4;  // rows per batch per warp (register budget)
     const int lane = ctid & 31, cw = ctid >> 5;
     const int layer = __ldg(ins + 1), kv_head = __ldg(ins + 2), num_partials = __ldg(ins + 3), part = __ldg(ins + 4);
     const int D = p.hd;
@@ -551,11 +764,23 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
     const bf16 *vbase = p.v_cache + layer_off;
     const int my_first = t0 + cw;
 
+    // Rows of earlier positions come from the cache (written by earlier launches);
+    // this token's row comes from the tagged cells its producers write in this launch.
+    const unsigned long long *k_new = p.t_k + ((size_t)layer * p.hkv * D + (size_t)kv_head * D + d0) / 2;
+    const unsigned long long *v_new = p.t_v + ((size_t)layer * p.hkv * D + (size_t)kv_head * D + d0) / 2;
     auto load_row = [&](uint4 (&kq)[V], uint4 (&vq)[V], int t) {
+        if (t == p.pos) {
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            kq[v] = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)t * tok_stride) + v);
-            vq[v] = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)t * tok_stride) + v);
+            for (int v = 0; v < V; ++v) {
+                load8_wait(p, s, k_new + 4 * v, tag, kq[v], 2, slot);
+                load8_wait(p, s, v_new + 4 * v, tag, vq[v], 2, slot);
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                kq[v] = __ldcg(reinterpret_cast<const uint4 *>(kbase + (size_t)t * tok_stride) + v);
+                vq[v] = __ldcg(reinterpret_cast<const uint4 *>(vbase + (size_t)t * tok_stride) + v);
+            }
         }
     };
 
@@ -581,9 +806,9 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
 
     uint4 q[V];
+    const unsigned long long *q_cells = p.t_q + ((size_t)layer * p.hq * D + (size_t)(kv_head * kGroup + h) * D + d0) / 2;
 #pragma unroll
-    for (int v = 0; v < V; ++v)
-        q[v] = __ldcg(reinterpret_cast<const uint4 *>(p.q_post + (size_t)(kv_head * kGroup + h) * D + d0) + v);
+    for (int v = 0; v < V; ++v) load8_wait(p, s, q_cells + 4 * v, tag, q[v], 2, slot);
     // the row appended by this launch, if it is one of those fetched early
 #pragma unroll
     for (int j = 0; j < kDepth; ++j) {
@@ -597,40 +822,57 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
     const float scale_log2e = p.attn_scale * 1.4426950408889634f;  // softmax in base 2; m is in log2 units
     if (ctid == 0) stamp(p, slot, 55, t_start);  // loop entry (loads issued, not yet consumed)
 
+    // Rows are taken in batches of kDepth per warp.  Within a batch all scores are
+    // computed first (independent dot products and shuffles), then one running-max
+    // update, then independent exponentials and accumulations: the only serial
+    // dependency is one max/rescale per batch instead of one per row.
     const int n_iter = (t1 - t0 + kConsumerWarps - 1) / kConsumerWarps;  // same for every warp
 #pragma unroll 1
     for (int base = 0; base < n_iter; base += kDepth) {
+        float sc[kDepth];
 #pragma unroll
         for (int j = 0; j < kDepth; ++j) {
-            if (base + j < n_iter) {
-                const int t = my_first + (base + j) * kConsumerWarps;
-                float d = 0.f;
-                float vf[DPL];
+            float d = 0.f;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                float kf[8];
+                unpack8(kq[j][v], kf);
+                d = dot8(q[v], kf, d);
+            }
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            const int t = my_first + (base + j) * kConsumerWarps;
+            sc[j] = (base + j < n_iter && t < t1) ? d * scale_log2e : -INFINITY;
+        }
+        float mn = m;
+#pragma unroll
+        for (int j = 0; j < kDepth; ++j) mn = fmaxf(mn, sc[j]);
+        if (mn > -INFINITY) {
+            const float corr = exp2f(m - mn);  // exp2(-inf) = 0 for the first batch
+            l *= corr;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+#pragma unroll
+            for (int j = 0; j < kDepth; ++j) {
+                const float pr = exp2f(sc[j] - mn);  // 0 for rows outside the slice
+                l += pr;
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
-                    float kf[8];
-                    unpack8(kq[j][v], kf);
-                    d = dot8(q[v], kf, d);
-                    float tmp[8];
-                    unpack8(vq[j][v], tmp);
+                    float vf[8];
+                    unpack8(vq[j][v], vf);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) vf[8 * v + i] = tmp[i];
+                    for (int i = 0; i < 8; ++i) acc[8 * v + i] = fmaf(pr, vf[i], acc[8 * v + i]);
                 }
-                const int t_next = t + kDepth * kConsumerWarps;
-                if (t_next < t1) load_row(kq[j], vq[j], t_next);
-                d += __shfl_xor_sync(0xffffffffu, d, 1);
-                d += __shfl_xor_sync(0xffffffffu, d, 2);
-                d += __shfl_xor_sync(0xffffffffu, d, 4);
-                if (t < t1) {
-                    const float sc = d * scale_log2e;
-                    const float mn = fmaxf(m, sc);
-                    const float corr = exp2f(m - mn);  // exp2(-inf) = 0 on the first row
-                    const float pr = exp2f(sc - mn);
-                    l = l * corr + pr;
+            }
+            m = mn;
+        }
+        // next batch (uniform condition: some warp still has rows)
+        if (base + kDepth < n_iter) {
 #pragma unroll
-                    for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pr, vf[i], acc[i] * corr);
-                    m = mn;
-                }
+            for (int j = 0; j < kDepth; ++j) {
+                const int t = my_first + (base + kDepth + j) * kConsumerWarps;
+                if (t < t1) load_row(kq[j], vq[j], t);
             }
         }
     }
@@ -661,25 +903,34 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
         }
         const float out = (L > 0.f) ? O / L : 0.f;
         const int head = kv_head * kGroup + h;
+        // neighbouring threads hold neighbouring dimensions: the even one writes the pair's cell
+        const float out_bf = round_bf16(out);
+        const float next_bf = __shfl_xor_sync(0xffffffffu, out_bf, 1);
         if (!aborted(s)) {
             if (p.skip_attn_reduction) {
                 p.attn_out[(size_t)head * D + d] = __float2bfloat16_rn(out);
+                if ((d & 1) == 0)
+                    st_tagged(p.t_attn + ((size_t)layer * p.hq * D + (size_t)head * D + d) / 2, pack_bf16x2(out_bf, next_bf), tag);
             } else {
                 p.attn_oi[((size_t)head * p.max_partials + part) * D + d] = out;
+                st_tagged(p.t_oi + (((size_t)layer * p.hq + head) * kTaggedPartials + part) * D + d, __float_as_uint(out), tag);
                 // log2 of the natural-exponent sum (reference python_vm.py:323); M is already in log2 units
-                if (d == 0)
-                    p.attn_lse[(size_t)head * p.max_partials + part] = (L > 0.f) ? M + log2f(L) : -INFINITY;
+                if (d == 0) {
+                    const float lse = (L > 0.f) ? M + log2f(L) : -INFINITY;
+                    p.attn_lse[(size_t)head * p.max_partials + part] = lse;
+                    st_tagged(p.t_lse + ((size_t)layer * p.hq + head) * kTaggedPartials + part, __float_as_uint(lse), tag);
+                }
             }
         }
     }
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);  // all stores issued; s.attn reusable
     if (ctid == 0) stamp(p, slot, 58, t_start);  // outputs stored
     if (ctid == 0 && !aborted(s)) {
+        // hints only: consumers validate the cells themselves
         if (p.skip_attn_reduction) {
-            red_release_gpu_add(counter(p, layer, 2, 0), kGroup);
+            red_relaxed_gpu_add(counter(p, layer, 2, 0), kGroup);
         } else {
-            fence_acq_rel_gpu();
-            for (int h = 0; h < kGroup; ++h) red_relaxed_gpu_add(counter(p, layer, 1, kv_head * kGroup + h), 1);
+            for (int hh = 0; hh < kGroup; ++hh) red_relaxed_gpu_add(counter(p, layer, 1, kv_head * kGroup + hh), 1);
         }
         stamp(p, slot, kEvOutputReady, t_start);
     }
@@ -688,7 +939,8 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, const int 
 // Log-sum-exp merge of attention partials for 4 heads (reference
 // python_vm.py:349-393).  Weights are exp2(lse - max); a non-terminal merge
 // stores the natural log of the weight sum as the reference does.
-__device__ void attention_reduction(const Params &p, Smem &s, int ctid, const int *ins, int slot, long long t_start) {
+__device__ void attention_reduction(const Params &p, Smem &s, int ctid, uint32_t tag, const int *ins, int slot,
+                                    long long t_start) {
     const int layer = __ldg(ins + 1), head0 = __ldg(ins + 2), num_partials = __ldg(ins + 3);
     const int terminal = __ldg(ins + 4), n = __ldg(ins + 5);
     const int out_slot = __ldg(ins + 6 + n);
@@ -702,40 +954,52 @@ __device__ void attention_reduction(const Params &p, Smem &s, int ctid, const in
     for (int idx = ctid; idx < kGroup * D; idx += kConsumerThreads) {
         const int h = idx / D, d = idx % D;
         const int head = head0 + h;
-        const float *lse = p.attn_lse + (size_t)head * p.max_partials;
-        const float *oi = p.attn_oi + (size_t)head * p.max_partials * D + d;
+        const unsigned long long *lse = p.t_lse + ((size_t)layer * p.hq + head) * kTaggedPartials;
+        const unsigned long long *oi = p.t_oi + (((size_t)layer * p.hq + head) * kTaggedPartials) * D + d;
         float mx = -INFINITY;
-        for (int j = 0; j < n; ++j) mx = fmaxf(mx, __ldcg(lse + __ldg(ins + 6 + j)));
+        for (int j = 0; j < n; ++j)
+            mx = fmaxf(mx, __uint_as_float(load1_wait(p, s, lse + __ldg(ins + 6 + j), tag, 3, slot)));
         float denom = 0.f, num = 0.f;
         for (int j = 0; j < n; ++j) {
             const int src = __ldg(ins + 6 + j);
-            const float f = exp2f(__ldcg(lse + src) - mx);
+            const float f = exp2f(__uint_as_float(load1_wait(p, s, lse + src, tag, 3, slot)) - mx);
             denom += f;
-            num = fmaf(__ldcg(oi + (size_t)src * D), f, num);
+            num = fmaf(__uint_as_float(load1_wait(p, s, oi + (size_t)src * D, tag, 3, slot)), f, num);
         }
         const float out = num / denom;
+        const float out_bf = round_bf16(out);
+        const float next_bf = __shfl_xor_sync(0xffffffffu, out_bf, 1);
         if (!aborted(s)) {
             if (terminal) {
                 p.attn_out[(size_t)head * D + d] = __float2bfloat16_rn(out);
+                if ((d & 1) == 0)
+                    st_tagged(p.t_attn + ((size_t)layer * p.hq * D + (size_t)head * D + d) / 2, pack_bf16x2(out_bf, next_bf), tag);
             } else {
+                // intermediate merge level (the schedule builders here only emit terminal merges)
                 p.attn_oi[((size_t)head * p.max_partials + out_slot) * D + d] = out;
-                if (d == 0) p.attn_lse[(size_t)head * p.max_partials + out_slot] = logf(denom);
+                st_tagged(p.t_oi + (((size_t)layer * p.hq + head) * kTaggedPartials + out_slot) * D + d, __float_as_uint(out), tag);
+                if (d == 0) {
+                    p.attn_lse[(size_t)head * p.max_partials + out_slot] = logf(denom);
+                    st_tagged(p.t_lse + ((size_t)layer * p.hq + head) * kTaggedPartials + out_slot, __float_as_uint(logf(denom)), tag);
+                }
             }
         }
     }
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
     if (ctid == 0 && !aborted(s)) {
-        red_release_gpu_add(counter(p, layer, 2, 0), kGroup);
+        red_relaxed_gpu_add(counter(p, layer, 2, 0), kGroup);
         stamp(p, slot, kEvOutputReady, t_start);
     }
 }
 
-template <int NCH>
+template <int NCH, bool FP4>
 __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_start) {
     const int lane = ctid & 31, cw = ctid >> 5;
-    ConsumerState st;
-    const bf16 *token_row = nullptr;
-    if (p.flags & MK_STEP_EMBED) token_row = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
+    ConsumerState<FP4> st;
+    const uint32_t tag = __ldg(p.epoch);
+    // layer-0 input: the embedding row of the fed-back token, or the host-written hidden state
+    const bf16 *step_input = p.hidden_states;
+    if (p.flags & MK_STEP_EMBED) step_input = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
 
 #pragma unroll 1
     for (int slot = 0; slot < p.queue_len; ++slot) {
@@ -752,27 +1016,28 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
                 consumer_wait(p, s, ctid, counter(p, layer - 1, 5, 0), p.down_total, op, slot);
                 if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
             }
-            const bf16 *base = (layer == 0 && token_row) ? token_row : p.hidden_states;
-            load_normed<NCH>(p, s, ctid, st.norm_toggle, base, layer > 0, p.attn_norm_w + (size_t)layer * p.hidden, x);
+            load_normed<NCH, FP4>(p, s, ctid, st.norm_toggle, tag, layer == 0 ? step_input : nullptr,
+                                  p.t_hidden + (size_t)(layer - 1) * (p.hidden / 2),
+                                  p.attn_norm_w + (size_t)layer * p.hidden, x, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
-            for (int b = b0; b < b1; ++b) consume_block<NCH>(p, s, st, lane, cw, x, op, slot);
+            for (int b = b0; b < b1; ++b) consume_block<NCH, FP4>(p, s, st, lane, cw, x, op, slot);
             break;
         }
         case 2:
-            if (p.hd == 64) attention_partial<8>(p, s, ctid, ins, slot, t_start);
-            else attention_partial<16>(p, s, ctid, ins, slot, t_start);
+            if (p.hd == 64) attention_partial<8>(p, s, ctid, tag, ins, slot, t_start);
+            else attention_partial<16>(p, s, ctid, tag, ins, slot, t_start);
             break;
         case 3:
-            attention_reduction(p, s, ctid, ins, slot, t_start);
+            attention_reduction(p, s, ctid, tag, ins, slot, t_start);
             break;
         case 4: {
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, layer, 2, 0), p.hq, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-            load_plain<NCH>(p.attn_out, ctid, x);
+            load_operand<NCH, FP4>(p, s, p.t_attn + (size_t)layer * (p.hq * p.hd / 2), tag, ctid, x, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
-            for (int b = b0; b < b1; ++b) consume_block<NCH>(p, s, st, lane, cw, x, op, slot);
+            for (int b = b0; b < b1; ++b) consume_block<NCH, FP4>(p, s, st, lane, cw, x, op, slot);
             break;
         }
         case 5: {
@@ -780,11 +1045,12 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, layer, 3, 0), p.hidden / kBlockRows, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-            load_normed<NCH>(p, s, ctid, st.norm_toggle, p.hidden_states, false, p.mlp_norm_w + (size_t)layer * p.hidden, x);
+            load_normed<NCH, FP4>(p, s, ctid, st.norm_toggle, tag, nullptr, p.t_resid + (size_t)layer * (p.hidden / 2),
+                                  p.mlp_norm_w + (size_t)layer * p.hidden, x, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
             for (int i = 0; i < n; ++i) {
-                consume_block<NCH>(p, s, st, lane, cw, x, op, slot);  // up rows
-                consume_block<NCH>(p, s, st, lane, cw, x, op, slot);  // gate rows
+                consume_block<NCH, FP4>(p, s, st, lane, cw, x, op, slot);  // up rows
+                consume_block<NCH, FP4>(p, s, st, lane, cw, x, op, slot);  // gate rows
             }
             break;
         }
@@ -795,9 +1061,9 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             consumer_wait(p, s, ctid, counter(p, layer, kSliceCounterRow, red), kChunkCols / kBlockRows, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
             uint4 xs[1][8];
-            load_plain<1>(p.silu_out + (size_t)red * kChunkCols, ctid, xs);
+            load_operand<1, FP4>(p, s, p.t_silu + ((size_t)layer * p.inter + (size_t)red * kChunkCols) / 2, tag, ctid, xs, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
-            for (int b = b0; b < b1; ++b) consume_block<1>(p, s, st, lane, cw, xs, op, slot);
+            for (int b = b0; b < b1; ++b) consume_block<1, FP4>(p, s, st, lane, cw, xs, op, slot);
             break;
         }
         case 7: {
@@ -805,9 +1071,10 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, p.layers - 1, 5, 0), p.down_total, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-            load_normed<NCH>(p, s, ctid, st.norm_toggle, p.hidden_states, true, p.lm_norm_w, x);
+            load_normed<NCH, FP4>(p, s, ctid, st.norm_toggle, tag, nullptr,
+                                  p.t_hidden + (size_t)(p.layers - 1) * (p.hidden / 2), p.lm_norm_w, x, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
-            for (int b = b0; b < b1; ++b) consume_block<NCH>(p, s, st, lane, cw, x, op, slot);
+            for (int b = b0; b < b1; ++b) consume_block<NCH, FP4>(p, s, st, lane, cw, x, op, slot);
             break;
         }
         default:
@@ -846,9 +1113,11 @@ __device__ __forceinline__ float collect_block(const Params &p, Smem &s, StorerS
     return v;
 }
 
+// Tells waiting consumers that `value` more blocks exist.  Only a hint (relaxed,
+// no fence): the cells themselves carry the launch tag.
 __device__ __forceinline__ void publish(const Params &p, Smem &s, int lane, int *ctr, int value) {
     __syncwarp();
-    if (lane == 0 && !aborted(s)) red_release_gpu_add(ctr, value);
+    if (lane == 0 && !aborted(s)) red_relaxed_gpu_add(ctr, value);
 }
 
 __device__ __forceinline__ unsigned long long argmax_key(float logit_bf16, int index) {
@@ -863,8 +1132,11 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
     StorerState st;
     const int D = p.hd;
     const int k_start = p.hq * D, v_start = k_start + p.hkv * D;
-    const bf16 *token_row = nullptr;
-    if (p.flags & MK_STEP_EMBED) token_row = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
+    const uint32_t tag = __ldg(p.epoch);
+    const bf16 *step_input = p.hidden_states;
+    if (p.flags & MK_STEP_EMBED) step_input = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
+    const bool writer = lane < kBlockRows;              // lanes that own an output row
+    const bool pair_writer = writer && (lane & 1) == 0;  // ... and write the cell of rows (lane, lane+1)
 
 #pragma unroll 1
     for (int slot = 0; slot < p.queue_len; ++slot) {
@@ -887,8 +1159,9 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                 pre_c[i] = __ldg(p.rope_cos + (size_t)p.pos * D + d);
                 pre_s[i] = __ldg(p.rope_sin + (size_t)p.pos * D + d);
             }
+            const float ts = matrix_scale(p.q_qkv, layer);
             for (int b = b0; b < b1; ++b) {
-                const float y = round_bf16(collect_block(p, s, st, lane, op, slot));
+                const float y = round_bf16(collect_block(p, s, st, lane, op, slot) * ts);
                 if (lane == 0 && b == b0) stamp(p, slot, kEvFirstStore, t_start);
                 const int row = b * kBlockRows + (lane & 15);
                 const float other = __shfl_xor_sync(0xffffffffu, y, 1);
@@ -900,19 +1173,29 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                     const float rot = (lane & 1) ? other : -other;
                     out = __fadd_rn(__fmul_rn(y, c), __fmul_rn(rot, sn));
                 }
-                if (lane < kBlockRows && !aborted(s)) {
+                out = round_bf16(out);
+                const float out_next = __shfl_xor_sync(0xffffffffu, out, 1);
+                if (writer && !aborted(s)) {
                     const bf16 o = __float2bfloat16_rn(out);
-                    if (row < k_start) p.q_post[row] = o;
-                    else if (row < v_start) p.k_cache[cache_row + (row - k_start)] = o;
-                    else p.v_cache[cache_row + (row - v_start)] = o;
+                    // the cache and q buffer serve later launches and the host; this
+                    // launch's attention reads the tagged cells
+                    unsigned long long *cell;
+                    if (row < k_start) {
+                        p.q_post[row] = o;
+                        cell = p.t_q + ((size_t)layer * k_start + row) / 2;
+                    } else if (row < v_start) {
+                        p.k_cache[cache_row + (row - k_start)] = o;
+                        cell = p.t_k + ((size_t)layer * (v_start - k_start) + (row - k_start)) / 2;
+                    } else {
+                        p.v_cache[cache_row + (row - v_start)] = o;
+                        cell = p.t_v + ((size_t)layer * (v_start - k_start) + (row - v_start)) / 2;
+                    }
+                    if (pair_writer) st_tagged(cell, pack_bf16x2(out, out_next), tag);
                 }
             }
-            // one counter per head; the first release also covers the later heads' rows
             const int bph = D / kBlockRows;
             __syncwarp();
-            if (lane == 0) stamp(p, slot, 59, t_start);  // outputs issued, before the fence
             if (lane == 0 && !aborted(s)) {
-                fence_acq_rel_gpu();  // once; the adds below are relaxed
                 for (int head = b0 / bph; head <= (b1 - 1) / bph; ++head) {
                     const int lo = max(b0, head * bph), hi = min(b1, (head + 1) * bph);
                     red_relaxed_gpu_add(counter(p, layer, 0, head), hi - lo);
@@ -921,29 +1204,25 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             break;
         }
         case 4: {
-            // hidden[rows] = bf16(hidden[rows] + bf16(matvec)) (reference python_vm.py:59-104)
+            // residual[rows] = bf16(residual[rows] + bf16(matvec)) (reference python_vm.py:59-104)
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
-            const bf16 *base = (layer == 0 && token_row) ? token_row : p.hidden_states;
+            // Residual stream entering this layer: the step input or the previous
+            // layer's output.  It is upstream of this instruction, so it is fetched
+            // (and waited for) before the sums arrive.
             auto residual = [&](int row) {
-                float h = ldcg_bf16(base + row);
-                if (layer > 0)
-                    for (int sl = 0; sl < p.down_slices; ++sl)
-                        h = round_bf16(h + ldcg_bf16(p.down_partials + (size_t)sl * p.hidden + row));
-                return h;
+                if (layer == 0) return ldcg_bf16(step_input + row);
+                const uint32_t pr = load1_wait(p, s, p.t_hidden + ((size_t)(layer - 1) * p.hidden + row) / 2, tag, op, slot);
+                return (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
             };
-            // The residual rows were finished by the previous layer.  If its last
-            // counter already shows that, fetch the first block's rows now instead
-            // of after the sums arrive (this warp is idle until then).
-            const bool early = layer == 0 || ld_acquire_gpu(counter(p, layer - 1, 5, 0)) >= p.down_total;
-            float h_first = 0.f;
-            if (early && lane < kBlockRows) h_first = residual(b0 * kBlockRows + lane);
+            const float ts = matrix_scale(p.q_o, layer);
+            float h = writer ? residual(b0 * kBlockRows + lane) : 0.f;
             for (int b = b0; b < b1; ++b) {
-                const float y = round_bf16(collect_block(p, s, st, lane, op, slot));
-                if (lane < kBlockRows && !aborted(s)) {
-                    const int row = b * kBlockRows + lane;
-                    const float h = (early && b == b0) ? h_first : residual(row);
-                    p.hidden_states[row] = __float2bfloat16_rn(h + y);
-                }
+                const float y = round_bf16(collect_block(p, s, st, lane, op, slot) * ts);
+                const float o = round_bf16(h + y);
+                const float o_next = __shfl_xor_sync(0xffffffffu, o, 1);
+                if (pair_writer && !aborted(s))
+                    st_tagged(p.t_resid + ((size_t)layer * p.hidden + b * kBlockRows + lane) / 2, pack_bf16x2(o, o_next), tag);
+                if (b + 1 < b1 && writer) h = residual((b + 1) * kBlockRows + lane);
             }
             publish(p, s, lane, counter(p, layer, 3, 0), b1 - b0);
             break;
@@ -951,21 +1230,25 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
         case 5: {
             // bf16(bf16(silu(bf16 gate)) * bf16 up) (reference python_vm.py:146-165)
             const int layer = __ldg(ins + 1), n = __ldg(ins + 2);
+            const float ts_up = matrix_scale(p.q_up, layer), ts_gate = matrix_scale(p.q_gate, layer);
             for (int i = 0; i < n; ++i) {
                 const int b = __ldg(ins + 3 + i);
-                const float up = round_bf16(collect_block(p, s, st, lane, op, slot));
-                const float gate = round_bf16(collect_block(p, s, st, lane, op, slot));
-                if (lane < kBlockRows && !aborted(s)) {
-                    const float act = round_bf16(gate / (1.0f + expf(-gate)));
-                    p.silu_out[b * kBlockRows + lane] = __float2bfloat16_rn(act * up);
+                const float up = round_bf16(collect_block(p, s, st, lane, op, slot) * ts_up);
+                const float gate = round_bf16(collect_block(p, s, st, lane, op, slot) * ts_gate);
+                float act = gate / (1.0f + expf(-gate));
+                if (!p.model_numerics) act = round_bf16(act);  // the interpreter rounds SiLU before the product
+                const float o = round_bf16(act * up);
+                const float o_next = __shfl_xor_sync(0xffffffffu, o, 1);
+                if (writer && !aborted(s)) {
+                    p.silu_out[b * kBlockRows + lane] = __float2bfloat16_rn(o);
+                    if (pair_writer)
+                        st_tagged(p.t_silu + ((size_t)layer * p.inter + b * kBlockRows + lane) / 2, pack_bf16x2(o, o_next), tag);
                 }
             }
-            // per 2048-column slice of silu_out (what one down-projection
+            // per 2048-column slice of the product (what one down-projection
             // instruction reads), then the reference interpreter's single counter
             const int my_slice = lane < n ? (__ldg(ins + 3 + lane) * kBlockRows) / kChunkCols : -1;
             __syncwarp();
-            if (lane == 0) stamp(p, slot, 59, t_start);  // outputs issued, before the fence
-            if (lane == 0) fence_acq_rel_gpu();  // once; the adds below are relaxed
             for (int sl = 0; sl < p.down_slices; ++sl) {
                 const int cnt = __popc(__ballot_sync(0xffffffffu, my_slice == sl));
                 if (lane == 0 && cnt && !aborted(s)) red_relaxed_gpu_add(counter(p, layer, kSliceCounterRow, sl), cnt);
@@ -974,13 +1257,53 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             break;
         }
         case 6: {
-            // bf16(matvec over one 2048-column slice), parked per slice; the
-            // consumers of the residual stream add the slices in slice order.
+            // fp32 sum over one 2048-column slice of a row block, parked per slice.
+            // The instruction that owns the LAST slice of a row block also folds all
+            // of that block's slices into the residual stream, always in slice order:
+            // with the interpreter's numerics each slice is rounded to bf16 and added
+            // with a bf16 rounding (its sequential `hidden += partial`,
+            // python_vm.py:59-80); with model numerics the slices are summed in fp32,
+            // scaled and rounded once.  The other slices are waited for cell by cell,
+            // so no ordering between the slice producers is needed.
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
+            const bool owner = red == p.down_slices - 1;
             for (int b = b0; b < b1; ++b) {
                 const float y = collect_block(p, s, st, lane, op, slot);
-                if (lane < kBlockRows && !aborted(s))
-                    p.down_partials[(size_t)red * p.hidden + b * kBlockRows + lane] = __float2bfloat16_rn(y);
+                const int row = b * kBlockRows + (lane & 15);
+                unsigned long long *parts = p.t_down + ((size_t)layer * p.down_slices) * p.hidden + row;
+                if (writer && !aborted(s)) st_tagged(parts + (size_t)red * p.hidden, __float_as_uint(y), tag);
+                if (!owner) continue;
+                float h = 0.f;
+                if (writer) {
+                    // one attempt on everything at once, then wait for what is missing
+                    const unsigned long long *rcell = p.t_resid + ((size_t)layer * p.hidden + row) / 2;
+                    unsigned long long rv = ld_tagged1(rcell);
+                    unsigned long long pv[kMaxDownSlices];
+#pragma unroll
+                    for (int sl = 0; sl < kMaxDownSlices; ++sl)
+                        if (sl < red) pv[sl] = ld_tagged1(parts + (size_t)sl * p.hidden);
+                    uint32_t pr = tag_payload(rv);
+                    if (!tag_ok(rv, tag)) pr = load1_wait(p, s, rcell, tag, op, slot);
+                    h = (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
+                    float total = 0.f;
+#pragma unroll
+                    for (int sl = 0; sl < kMaxDownSlices; ++sl) {
+                        if (sl <= red) {
+                            float part = y;
+                            if (sl < red) {
+                                uint32_t bits = tag_payload(pv[sl]);
+                                if (!tag_ok(pv[sl], tag)) bits = load1_wait(p, s, parts + (size_t)sl * p.hidden, tag, op, slot);
+                                part = __uint_as_float(bits);
+                            }
+                            if (p.model_numerics) total += part;
+                            else h = round_bf16(h + round_bf16(part));
+                        }
+                    }
+                    if (p.model_numerics) h = round_bf16(h + round_bf16(total * down_scale(p, layer)));
+                }
+                const float h_next = __shfl_xor_sync(0xffffffffu, h, 1);
+                if (pair_writer && !aborted(s))
+                    st_tagged(p.t_hidden + ((size_t)layer * p.hidden + row) / 2, pack_bf16x2(h, h_next), tag);
             }
             publish(p, s, lane, counter(p, layer, 5, 0), b1 - b0);
             break;
@@ -988,8 +1311,9 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
         case 7: {
             const int b0 = __ldg(ins + 1), b1 = __ldg(ins + 2);
             unsigned long long best = 0ull;
+            const float ts = matrix_scale(p.q_lm, 0);
             for (int b = b0; b < b1; ++b) {
-                const float y = round_bf16(collect_block(p, s, st, lane, op, slot));
+                const float y = round_bf16(collect_block(p, s, st, lane, op, slot) * ts);
                 if (lane < kBlockRows && !aborted(s)) {
                     const int row = b * kBlockRows + lane;
                     p.logits[row] = __float2bfloat16_rn(y);
@@ -1016,7 +1340,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
 // kernel
 // ---------------------------------------------------------------------------
 
-template <int NCH>
+template <int NCH, bool FP4>
 __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -1024,7 +1348,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const Params p
     const long long t_start = clock64();
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < Fmt<FP4>::stages; ++i) {
             mbar_init(&s.full[i], 1);
             mbar_init(&s.empty[i], kConsumerWarps);
         }
@@ -1039,10 +1363,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const Params p
     __syncthreads();
 
     if (warp == 0) {
-        if (lane == 0) loader_role<NCH>(p, s, t_start);
+        if (lane == 0) loader_role<NCH, FP4>(p, s, t_start);
         __syncwarp();
     } else if (warp < kStorerWarp) {
-        consumer_role<NCH>(p, s, tid - 32, t_start);
+        consumer_role<NCH, FP4>(p, s, tid - 32, t_start);
     } else {
         storer_role<NCH>(p, s, lane, t_start);
     }
@@ -1058,21 +1382,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const Params p
     __syncthreads();
     if (!s.is_last) return;
 
-    // Residual stream: fold in the last down-projection's slice sums unless an
-    // o_proj of the following layer already did.
-    int pending_layer = -1;
+    // Residual stream handed back to the host: the output of the last layer whose
+    // attention block completed - after its MLP block if that completed too.  With
+    // no completed block the step input is left as it is.
+    const uint32_t tag = __ldg(p.epoch);
+    int last = -1;
     for (int l = p.layers - 1; l >= 0; --l) {
-        if (ld_acquire_gpu(counter(p, l, 5, 0)) != 0) { pending_layer = l; break; }
+        if (ld_relaxed_gpu(counter(p, l, 3, 0)) >= p.hidden / kBlockRows) { last = l; break; }
     }
-    if (pending_layer >= 0 && ld_acquire_gpu(counter(p, pending_layer, 5, 0)) >= p.down_total &&
-        (pending_layer == p.layers - 1 || ld_acquire_gpu(counter(p, pending_layer + 1, 3, 0)) == 0)) {
+    if (last >= 0) {
+        const bool mlp_done = ld_relaxed_gpu(counter(p, last, 5, 0)) >= p.down_total;
+        const unsigned long long *src = (mlp_done ? p.t_hidden : p.t_resid) + (size_t)last * (p.hidden / 2);
         for (int idx = tid; idx < p.hidden; idx += kThreads) {
-            float h = ldcg_bf16(p.hidden_states + idx);
-            for (int sl = 0; sl < p.down_slices; ++sl)
-                h = round_bf16(h + ldcg_bf16(p.down_partials + (size_t)sl * p.hidden + idx));
-            p.hidden_states[idx] = __float2bfloat16_rn(h);
+            const uint32_t pr = tag_payload(ld_tagged1(src + idx / 2));
+            p.hidden_states[idx] = __float2bfloat16_rn((idx & 1) ? bf16_hi(pr) : bf16_lo(pr));
         }
     }
+    if (tid == 0) *p.epoch = (tag + 1u == 0u) ? 1u : tag + 1u;  // the next launch accepts none of this one's cells
     if (tid == 0) {
         const unsigned long long key = __ldcg(p.argmax_key);
         if ((p.flags & MK_STEP_WRITE_TOKEN) && p.token_out != nullptr)
@@ -1110,6 +1436,7 @@ struct Handle {
     Params params;
     int device = 0;
     int nch = 1;
+    bool fp4 = false;
     int sm_count = 0;
     int resident = 0;
     cudaFuncAttributes attrs;
@@ -1118,9 +1445,12 @@ struct Handle {
     size_t scratch_bytes = 0;
 };
 
-static const void *kernel_for(int nch) {
-    return nch == 2 ? reinterpret_cast<const void *>(&decode_step_kernel<2>)
-                    : reinterpret_cast<const void *>(&decode_step_kernel<1>);
+static const void *kernel_for(int nch, bool fp4) {
+    if (fp4)
+        return nch == 2 ? reinterpret_cast<const void *>(&decode_step_kernel<2, true>)
+                        : reinterpret_cast<const void *>(&decode_step_kernel<1, true>);
+    return nch == 2 ? reinterpret_cast<const void *>(&decode_step_kernel<2, false>)
+                    : reinterpret_cast<const void *>(&decode_step_kernel<1, false>);
 }
 
 }  // namespace mk
@@ -1144,8 +1474,9 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     *out = nullptr;
     if (d->abi_version != MK_ABI_VERSION)
         return fail(MK_ERR_BAD_ARGUMENT, "mk_create: ABI version %d, library has %d", d->abi_version, MK_ABI_VERSION);
-    if (d->weight_format != MK_WEIGHTS_BF16)
+    if (d->weight_format != MK_WEIGHTS_BF16 && d->weight_format != MK_WEIGHTS_NVFP4)
         return fail(MK_ERR_UNSUPPORTED, "mk_create: weight format %d not supported by this build", d->weight_format);
+    const bool fp4 = d->weight_format == MK_WEIGHTS_NVFP4;
     const int H = d->hidden_size, D = d->head_dim;
     if (H <= 0 || d->num_layers <= 0 || d->num_q_heads <= 0 || d->num_kv_heads <= 0 || D <= 0 ||
         d->intermediate_size <= 0 || d->vocab_size <= 0)
@@ -1162,7 +1493,25 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
         return fail(MK_ERR_BAD_ARGUMENT, "barriers tensor too small: rows %d cols %d", d->barrier_rows, d->barrier_cols);
     if (d->kv_batch < 1 || d->kv_max_len < 1 || d->rope_positions < 1 || d->max_partials < 1)
         return fail(MK_ERR_BAD_ARGUMENT, "mk_create: cache/rope/partials extent must be positive");
-    const void *required[] = {d->qkv_w, d->o_w, d->up_w, d->gate_w, d->down_w, d->lm_head_w, d->attn_norm_w,
+    if (fp4) {
+        const MkNvfp4Matrix *tables[] = {d->qkv_q, d->o_q, d->up_q, d->gate_q, d->down_q, d->lm_head_q};
+        for (int ti = 0; ti < 6; ++ti) {
+            if (!tables[ti]) return fail(MK_ERR_BAD_ARGUMENT, "mk_create: NVFP4 model without a quantised weight table");
+            const int count = ti == 5 ? 1 : d->num_layers;
+            for (int i = 0; i < count; ++i) {
+                const MkNvfp4Matrix &q = tables[ti][i];
+                if (!q.packed || !q.scales || (reinterpret_cast<uintptr_t>(q.packed) & 15) ||
+                    (reinterpret_cast<uintptr_t>(q.scales) & 15) || !(q.tensor_scale > 0.f))
+                    return fail(MK_ERR_BAD_ARGUMENT, "mk_create: NVFP4 matrix %d/%d: null or misaligned pointer, or non-positive scale", ti, i);
+            }
+        }
+    } else {
+        const void *weights[] = {d->qkv_w, d->o_w, d->up_w, d->gate_w, d->down_w, d->lm_head_w};
+        for (const void *ptr : weights)
+            if (!ptr || (reinterpret_cast<uintptr_t>(ptr) & 15))
+                return fail(MK_ERR_BAD_ARGUMENT, "mk_create: null or misaligned bf16 weight pointer");
+    }
+    const void *required[] = {d->attn_norm_w,
                               d->mlp_norm_w, d->lm_head_norm_w, d->k_cache, d->v_cache, d->rope_cos, d->rope_sin,
                               d->hidden_states, d->q_post_rope, d->attn_out, d->attn_lse_intermediates,
                               d->attn_out_intermediates, d->silu_out, d->logits, d->barriers};
@@ -1175,6 +1524,7 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     if (!h) return fail(MK_ERR_BAD_ARGUMENT, "mk_create: out of host memory");
     h->desc = *d;
     h->nch = H / kChunkCols;
+    h->fp4 = fp4;
     cudaError_t e = cudaGetDevice(&h->device);
     if (e != cudaSuccess) { delete h; return cuda_fail(e, "cudaGetDevice"); }
     cudaDeviceProp prop;
@@ -1183,7 +1533,7 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     h->sm_count = prop.multiProcessorCount;
     if (!prop.cooperativeLaunch) { delete h; return fail(MK_ERR_RESIDENCY, "device does not support cooperative launch"); }
 
-    const void *kern = kernel_for(h->nch);
+    const void *kern = kernel_for(h->nch, h->fp4);
     h->smem_bytes = sizeof(Smem) + 128;
     int optin = 0;
     cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, h->device);
@@ -1199,14 +1549,24 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     if (e != cudaSuccess) { delete h; return cuda_fail(e, "occupancy query"); }
     if (h->resident < 1) { delete h; return fail(MK_ERR_RESIDENCY, "kernel cannot keep one CTA resident per SM"); }
 
-    // scratch: [down_slices][hidden] bf16 | argmax key (8 B) | done counter | status[8]
+    // scratch: tagged cells | argmax key (8 B) | exit counter | status[8] | launch tag
     const int slices = d->intermediate_size / kChunkCols;
-    const size_t partial_bytes = ((size_t)slices * H * sizeof(bf16) + 255) & ~size_t(255);
-    h->scratch_bytes = partial_bytes + 256;
+    if (slices > kMaxDownSlices) { delete h; return fail(MK_ERR_UNSUPPORTED, "intermediate_size %d: at most %d column slices", d->intermediate_size, kMaxDownSlices); }
+    const size_t L = d->num_layers, qd = (size_t)d->num_q_heads * D, kvd = (size_t)d->num_kv_heads * D;
+    const size_t n_resid = L * H / 2, n_hidden = L * H / 2, n_down = L * slices * H, n_q = L * qd / 2, n_kv = L * kvd / 2, n_attn = L * qd / 2;
+    const size_t n_silu = L * d->intermediate_size / 2, n_oi = L * d->num_q_heads * kTaggedPartials * D;
+    const size_t n_lse = L * d->num_q_heads * kTaggedPartials;
+    const size_t cells = n_resid + n_hidden + n_down + n_q + 2 * n_kv + n_attn + n_silu + n_oi + n_lse;
+    const size_t cell_bytes = (cells * sizeof(unsigned long long) + 255) & ~size_t(255);
+    const size_t table_entries = fp4 ? 5 * L + 1 : 0;  // device copies of the quantised-matrix tables
+    h->scratch_bytes = cell_bytes + 256 + table_entries * sizeof(MkNvfp4Matrix);
     e = cudaMalloc(&h->scratch, h->scratch_bytes);
     if (e != cudaSuccess) { delete h; return cuda_fail(e, "cudaMalloc(scratch)"); }
-    e = cudaMemset(h->scratch, 0, h->scratch_bytes);
+    e = cudaMemset(h->scratch, 0, h->scratch_bytes);  // tag 0 is never a launch tag
     if (e != cudaSuccess) { cudaFree(h->scratch); delete h; return cuda_fail(e, "cudaMemset(scratch)"); }
+    const unsigned first_tag = 1;
+    e = cudaMemcpy((uint8_t *)h->scratch + cell_bytes + 64, &first_tag, sizeof(first_tag), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(h->scratch); delete h; return cuda_fail(e, "cudaMemcpy(launch tag)"); }
 
     Params &p = h->params;
     memset(&p, 0, sizeof(p));
@@ -1232,10 +1592,35 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.silu_out = (bf16 *)d->silu_out; p.logits = (bf16 *)d->logits;
     p.bar = d->barriers;
     uint8_t *sc = (uint8_t *)h->scratch;
-    p.down_partials = (bf16 *)sc;
-    p.argmax_key = (unsigned long long *)(sc + partial_bytes);
-    p.done_counter = (int *)(sc + partial_bytes + 16);
-    p.status = (int *)(sc + partial_bytes + 32);
+    unsigned long long *cell = (unsigned long long *)sc;
+    p.t_resid = cell; cell += n_resid;
+    p.t_hidden = cell; cell += n_hidden;
+    p.t_down = cell;  cell += n_down;
+    p.t_q = cell;     cell += n_q;
+    p.t_k = cell;     cell += n_kv;
+    p.t_v = cell;     cell += n_kv;
+    p.t_attn = cell;  cell += n_attn;
+    p.t_silu = cell;  cell += n_silu;
+    p.t_oi = cell;    cell += n_oi;
+    p.t_lse = cell;   cell += n_lse;
+    p.argmax_key = (unsigned long long *)(sc + cell_bytes);
+    p.done_counter = (int *)(sc + cell_bytes + 16);
+    p.status = (int *)(sc + cell_bytes + 32);
+    p.epoch = (unsigned *)(sc + cell_bytes + 64);
+    p.model_numerics = fp4 ? 1 : 0;
+    if (fp4) {
+        MkNvfp4Matrix *dev = (MkNvfp4Matrix *)(sc + cell_bytes + 256);
+        const MkNvfp4Matrix *src[] = {d->qkv_q, d->o_q, d->up_q, d->gate_q, d->down_q};
+        const MkNvfp4Matrix **dst[] = {&p.q_qkv, &p.q_o, &p.q_up, &p.q_gate, &p.q_down};
+        for (int ti = 0; ti < 5; ++ti) {
+            e = cudaMemcpy(dev + ti * L, src[ti], L * sizeof(MkNvfp4Matrix), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) { cudaFree(h->scratch); delete h; return cuda_fail(e, "cudaMemcpy(weight table)"); }
+            *dst[ti] = dev + ti * L;
+        }
+        e = cudaMemcpy(dev + 5 * L, d->lm_head_q, sizeof(MkNvfp4Matrix), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { cudaFree(h->scratch); delete h; return cuda_fail(e, "cudaMemcpy(weight table)"); }
+        p.q_lm = dev + 5 * L;
+    }
     *out = h;
     return 0;
 }
@@ -1277,7 +1662,7 @@ extern "C" int mk_step(void *handle, int32_t pos_id, uint32_t flags, const int32
     p.token_in = token_in;
     p.token_out = token_out;
     void *args[] = {&p};
-    cudaError_t e = cudaLaunchCooperativeKernel(kernel_for(h->nch), dim3(p.workers), dim3(kThreads), args,
+    cudaError_t e = cudaLaunchCooperativeKernel(kernel_for(h->nch, h->fp4), dim3(p.workers), dim3(kThreads), args,
                                                 h->smem_bytes, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "cooperative megakernel launch");
     return 0;
@@ -1297,8 +1682,8 @@ extern "C" int mk_query(void *handle, MkLaunchInfo *info) {
     info->local_bytes_per_thread = (int)h->attrs.localSizeBytes;
     info->static_smem_bytes = (int)h->attrs.sharedSizeBytes;
     info->dynamic_smem_bytes = (int)h->smem_bytes;
-    info->stage_count = kStages;
-    info->stage_bytes = kStageBytes;
+    info->stage_count = h->fp4 ? kFp4Stages : kStages;
+    info->stage_bytes = h->fp4 ? kFp4TileBytes : kStageBytes;
     info->resident_ctas_per_sm = h->resident;
     info->queue_len = h->params.queue_len;
     info->scratch_bytes = (int64_t)h->scratch_bytes;
@@ -1319,7 +1704,7 @@ extern "C" int mk_status(void *handle, MkStatus *status, void *stream) {
     }
     if (words[0] != 0 || words[7] != 0) {
         // leave the handle reusable: clear status, argmax cell and the exit counter
-        cudaMemset(h->params.argmax_key, 0, 256);
+        cudaMemset(h->params.argmax_key, 0, 64);
         return fail(MK_ERR_DEVICE_WAIT, "device wait expired: code %d worker %d opcode %d slot %d saw %d expected %d",
                     words[0], words[1], words[2], words[3], words[4], words[5]);
     }

@@ -112,6 +112,34 @@ __device__ __forceinline__ void red_relaxed_gpu_add(int *p, int v) {
 }
 
 // ---------------------------------------------------------------------------
+// tagged words: 32 bits of payload and a 32-bit launch tag in one 8-byte cell
+// ---------------------------------------------------------------------------
+// Activations that cross SMs inside a launch travel in 8-byte cells written and
+// read with single 64-bit accesses.  A reader accepts a cell only if its tag is
+// the current launch's, so payload and "it has been written" arrive together:
+// no fence is needed between producing data and telling consumers about it.
+
+__device__ __forceinline__ void st_tagged(unsigned long long *cell, uint32_t payload, uint32_t tag) {
+    const unsigned long long v = ((unsigned long long)tag << 32) | payload;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(cell), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ ulonglong2 ld_tagged2(const unsigned long long *cell) {
+    ulonglong2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(cell) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long ld_tagged1(const unsigned long long *cell) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cell) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ bool tag_ok(unsigned long long v, uint32_t tag) { return (uint32_t)(v >> 32) == tag; }
+__device__ __forceinline__ uint32_t tag_payload(unsigned long long v) { return (uint32_t)v; }
+
+// ---------------------------------------------------------------------------
 // bf16 helpers
 // ---------------------------------------------------------------------------
 

@@ -157,6 +157,10 @@ static cudaError_t launch_gemv(const void *w, const void *packed, const void *sc
     return cudaGetLastError();
 }
 
+// tensor-core path (gemv.cu); needs k to be a multiple of 256
+cudaError_t launch_gemv_mma(const void *w, const void *packed, const void *scales, const void *x, void *y, int m, int k,
+                            float ts, int is_packed, int batch, cudaStream_t stream);
+
 }  // namespace mk
 
 extern "C" int mk_nvfp4_quantize(const void *input_bf16, void *packed, void *scales, float *decoded, int32_t rows,
@@ -174,8 +178,12 @@ extern "C" int mk_nvfp4_quantize(const void *input_bf16, void *packed, void *sca
 extern "C" int mk_gemv(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y, int32_t m,
                        int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream) {
     if (!x || !y || m <= 0 || k <= 0 || (k % 32) != 0 || batch < 1 || batch > 8) return cudaErrorInvalidValue;
+    if (is_packed ? (!packed || !scales) : !w_bf16) return cudaErrorInvalidValue;
+    if (k % 256 == 0)
+        return (int)mk::launch_gemv_mma(w_bf16, packed, scales, x, y, m, k, tensor_scale, is_packed, batch,
+                                        (cudaStream_t)stream);
+    // odd widths: plain warp-per-row kernel
     if (is_packed) {
-        if (!packed || !scales) return cudaErrorInvalidValue;
         return (int)mk::launch_gemv<true>(nullptr, packed, scales, x, y, m, k, tensor_scale, batch, (cudaStream_t)stream);
     }
     if (!w_bf16) return cudaErrorInvalidValue;

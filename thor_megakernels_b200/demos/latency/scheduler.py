@@ -134,7 +134,9 @@ def schedule_downproj(globs: Globals, layer_idx: int):
     """(column slice, row block) jobs in column-major order, dealt out evenly;
     an instruction never straddles two column slices."""
     row_blocks = assert_div(globs.hidden_size, globs.down_proj_block_size)
-    col_slices = globs.intermediate_size // globs.hidden_size
+    # 2048-column slices of the input; equals intermediate_size // hidden_size (the
+    # reference's expression) whenever hidden_size is 2048
+    col_slices = assert_div(globs.intermediate_size, globs.matvec_reduction_size)
     workers = globs.sm_count()
     jobs = [(c, r) for c in range(col_slices) for r in range(row_blocks)]
 

@@ -95,7 +95,9 @@ class MK_Generator(Generator):
 class MK_FusedGenerator(Generator):
     """Decode loop with no per-token host work beyond one launch."""
 
-    def __init__(self, model, schedule: Schedule):
+    def __init__(self, model, schedule: Schedule, quantized: dict | None = None):
+        """``quantized``: result of ``nvfp4.quantize_model(model)`` to decode with
+        NVFP4 weight-only linears instead of the bf16 weights."""
         from .runtime import Megakernel
 
         self.model = model
@@ -103,7 +105,8 @@ class MK_FusedGenerator(Generator):
         globs = schedule.globs
         if globs.instructions is None:
             raise ValueError("schedule has no instruction tensor; call tensorize_instructions first")
-        self.mk = Megakernel.from_globals(globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data)
+        self.mk = Megakernel.from_globals(globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data,
+                                          quantized=quantized)
         globs.barriers.zero_()
 
     def generate(self, output_tokens: Tensor, prompt_len: int, ntok: int, ntok_already_generated: int = 1):

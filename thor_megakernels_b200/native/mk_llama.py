@@ -37,7 +37,9 @@ def mk_llama(
     tensors = (Bar, qkv_weights, attn_norm_weights, o_weights, mlp_norm_weights, up_weights, gate_weights,
                down_weights, lm_head_norm_weights, lm_head_weights, k_cache, v_cache, rope_cos, rope_sin,
                hidden_states, q_post_rope, attn_out, attn_lse_intermediates, attn_out_intermediates, silu_out, logits)
-    key = tuple(t.data_ptr() for t in tensors) + (float(attn_scale), float(rms_norm_eps), bool(skip_attn_reduction))
+    # addresses alone are not an identity: the allocator hands freed blocks to new tensors
+    key = tuple((t.data_ptr(), tuple(t.shape)) for t in tensors) + (
+        float(attn_scale), float(rms_norm_eps), bool(skip_attn_reduction))
     mk = _cache.get(key)
     if mk is None:
         if len(_cache) >= 8:  # a long-lived process that keeps re-allocating buffers

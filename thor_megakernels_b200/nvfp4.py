@@ -84,3 +84,22 @@ def gemv(weight: Nvfp4Weight | torch.Tensor, x: torch.Tensor, out: torch.Tensor 
     if code != 0:
         raise _lib.MegakernelError(code, f"mk_gemv refused m={rows} k={k} batch={batch}")
     return y.view(-1) if squeeze and out is None else y
+
+
+def quantize_model(model) -> dict:
+    """Quantise every linear of a finalised model container for the NVFP4
+    weight-only megakernel: per layer qkv, o, up, gate, down and the LM head.
+    up and gate share the tensor scale of their concatenation, as in the
+    reference's plan where they are one matrix
+    (experimental/native_fp4_vm/model.cu:112-126)."""
+    sp = model.stacked_params
+    out = {k: [] for k in ("qkv", "o", "up", "gate", "down")}
+    for i in range(model.config.num_hidden_layers):
+        ug = float(np.float32(max(max(sp.up_proj[i].abs().max().item(), sp.gate_proj[i].abs().max().item()) / (6 * 448), 1e-12)))
+        out["qkv"].append(quantize_weight(sp.qkv_proj[i].contiguous()))
+        out["o"].append(quantize_weight(sp.o_proj[i].contiguous()))
+        out["up"].append(quantize_weight(sp.up_proj[i].contiguous(), ug))
+        out["gate"].append(quantize_weight(sp.gate_proj[i].contiguous(), ug))
+        out["down"].append(quantize_weight(sp.down_proj[i].contiguous()))
+    out["lm_head"] = quantize_weight(model.lm_head.lm_head.weight.data.contiguous())
+    return out

@@ -46,11 +46,18 @@ class Megakernel:
         k_cache, v_cache, rope_cos, rope_sin, hidden_states, q_post_rope, attn_out,
         attn_lse_intermediates, attn_out_intermediates, silu_out, logits,
         attn_scale: float, rms_norm_eps: float, skip_attn_reduction: bool = True,
-        embed_w=None, num_kv_heads: int | None = None,
+        embed_w=None, num_kv_heads: int | None = None, quantized: dict | None = None,
     ):
+        """``quantized``: for an NVFP4 weight-only model, a dict with lists of
+        ``Nvfp4Weight`` per layer under ``qkv``, ``o``, ``up``, ``gate``, ``down`` and
+        one under ``lm_head``; the bf16 weight arguments then only supply shapes
+        and may be dropped by the caller afterwards."""
         bf16, f32, i32 = torch.bfloat16, torch.float32, torch.int32
-        for name, t in dict(qkv_w=qkv_w, attn_norm_w=attn_norm_w, o_w=o_w, mlp_norm_w=mlp_norm_w, up_w=up_w,
-                            gate_w=gate_w, down_w=down_w, lm_head_norm_w=lm_head_norm_w, lm_head_w=lm_head_w,
+        weights = dict(qkv_w=qkv_w, o_w=o_w, up_w=up_w, gate_w=gate_w, down_w=down_w, lm_head_w=lm_head_w)
+        if quantized is None:
+            for name, t in weights.items():
+                _require(t, name, bf16)
+        for name, t in dict(attn_norm_w=attn_norm_w, mlp_norm_w=mlp_norm_w, lm_head_norm_w=lm_head_norm_w,
                             k_cache=k_cache, v_cache=v_cache, hidden_states=hidden_states,
                             q_post_rope=q_post_rope, attn_out=attn_out, silu_out=silu_out, logits=logits).items():
             _require(t, name, bf16)
@@ -82,12 +89,27 @@ class Megakernel:
         self.lib = _lib.load()
         d = _lib.MkModelDesc()
         d.abi_version = _lib.MK_ABI_VERSION
-        d.weight_format = _lib.MK_WEIGHTS_BF16
+        d.weight_format = _lib.MK_WEIGHTS_BF16 if quantized is None else _lib.MK_WEIGHTS_NVFP4
         d.hidden_size, d.num_layers, d.num_q_heads, d.num_kv_heads = hidden, layers, q_heads, kv_heads
         d.head_dim, d.intermediate_size, d.vocab_size = head_dim, inter, lm_head_w.shape[0]
         d.attn_scale, d.rms_norm_eps = float(attn_scale), float(rms_norm_eps)
-        d.qkv_w, d.o_w, d.up_w, d.gate_w, d.down_w = map(_ptr, (qkv_w, o_w, up_w, gate_w, down_w))
-        d.lm_head_w, d.attn_norm_w, d.mlp_norm_w = map(_ptr, (lm_head_w, attn_norm_w, mlp_norm_w))
+        if quantized is None:
+            d.qkv_w, d.o_w, d.up_w, d.gate_w, d.down_w = map(_ptr, (qkv_w, o_w, up_w, gate_w, down_w))
+            d.lm_head_w = _ptr(lm_head_w)
+        else:
+            self._tables = {}
+            for key, field in (("qkv", "qkv_q"), ("o", "o_q"), ("up", "up_q"), ("gate", "gate_q"), ("down", "down_q"),
+                               ("lm_head", "lm_head_q")):
+                mats = quantized[key] if key != "lm_head" else [quantized[key]]
+                if key != "lm_head" and len(mats) != layers:
+                    raise ValueError(f"quantized[{key!r}] needs one matrix per layer")
+                table = (_lib.MkNvfp4Matrix * len(mats))()
+                for i, m in enumerate(mats):
+                    table[i].packed, table[i].scales = m.packed.data_ptr(), m.scales.data_ptr()
+                    table[i].tensor_scale = float(m.tensor_scale)
+                self._tables[key] = (table, mats)  # keep the ctypes arrays and the tensors alive
+                setattr(d, field, table)
+        d.attn_norm_w, d.mlp_norm_w = map(_ptr, (attn_norm_w, mlp_norm_w))
         d.lm_head_norm_w, d.embed_w = _ptr(lm_head_norm_w), _ptr(embed_w)
         d.k_cache, d.v_cache, d.kv_batch, d.kv_max_len = _ptr(k_cache), _ptr(v_cache), kv_batch, kv_len
         d.rope_cos, d.rope_sin, d.rope_positions = _ptr(rope_cos), _ptr(rope_sin), rope_cos.shape[0]
@@ -107,7 +129,7 @@ class Megakernel:
 
     # -- construction from the schedule's table ---------------------------
     @classmethod
-    def from_globals(cls, globs, embed_w=None) -> "Megakernel":
+    def from_globals(cls, globs, embed_w=None, quantized: dict | None = None) -> "Megakernel":
         mk = cls(
             barriers=globs.barriers, qkv_w=globs.qkv_proj_weights, attn_norm_w=globs.attn_ln_weights,
             o_w=globs.o_proj_weights, mlp_norm_w=globs.mlp_ln_weights, up_w=globs.up_proj_weights,
@@ -118,7 +140,7 @@ class Megakernel:
             attn_lse_intermediates=globs.attn_lse_intermediates,
             attn_out_intermediates=globs.attn_out_intermediates, silu_out=globs.silu_out, logits=globs.logits,
             attn_scale=globs.attn_scale, rms_norm_eps=globs.rms_norm_eps,
-            skip_attn_reduction=globs.skip_attn_reduction, embed_w=embed_w,
+            skip_attn_reduction=globs.skip_attn_reduction, embed_w=embed_w, quantized=quantized,
         )
         if globs.instructions is not None:
             mk.set_schedule(globs.instructions, globs.timings)
