@@ -225,6 +225,20 @@ int mk_nvfp4_quantize(const void *input_bf16, void *packed, void *scales, float 
 int mk_gemv(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y,
             int32_t m, int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream);
 
+/*
+ * mk_gemv without any allocation (no reference counterpart: the reference has
+ * no such call).  Same arguments and results as mk_gemv, but the split-K
+ * scratch is a fixed 4 MiB + 16 KiB array inside the library, so the call never
+ * reaches cudaMalloc/cudaFree.  Limits: k a multiple of 256; when k > 2048,
+ * ceil(m/16) <= 4096 and ceil(k/2048) * 8 * m <= 1048576 (e.g. 8192 x 8192,
+ * 16384 x 16384); beyond that MK_ERR_UNSUPPORTED with the sizes in
+ * mk_last_error().  The array is shared per device: calls that overlap in time
+ * race on it.  The first call on a device resolves the array's address and
+ * must happen outside stream capture.
+ */
+int mk_gemv_static(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y,
+                   int32_t m, int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,7 @@ MK_WEIGHTS_NVFP4 = 1
 EXPORTED_SYMBOLS = [
     "mk_last_error", "mk_create", "mk_set_schedule", "mk_step", "mk_query", "mk_status",
     "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
+    "mk_gemv_static",
 ]
 
 
@@ -104,6 +105,7 @@ def load() -> C.CDLL:
     lib.mk_destroy.restype = None
     lib.mk_nvfp4_quantize.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
     lib.mk_gemv.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
+    lib.mk_gemv_static.argtypes = lib.mk_gemv.argtypes
     lib.mk_abi_sizeof.argtypes = [i32]
     lib.mk_set_option.argtypes = [vp, i32, C.c_int64]
     for name in EXPORTED_SYMBOLS:

@@ -187,4 +187,85 @@ cudaError_t launch_gemv_mma(const void *w, const void *packed, const void *scale
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// mk_gemv_static: the same GEMV with its split-K scratch in a fixed array of the
+// module instead of lazily allocated memory, so the call allocates nothing.
+//
+// The array holds the row-block tickets (kStaticTickets ints) followed by the
+// fp32 partial sums (kStaticPartialFloats floats): 16 KiB + 4 MiB per device.
+// A call needs ceil(m/16) tickets and ceil(k/2048) * 8 * m partial floats when
+// k > 2048, nothing otherwise; larger problems are refused.
+//
+// The array is shared by every call on a device: two calls that overlap in time
+// (different streams, or different threads on one stream's worth of work) race
+// on it.  The first call on a device looks the array's address up, which is not
+// allowed while a stream is being captured, so make it before any capture.
+// ---------------------------------------------------------------------------
+constexpr int kStaticTickets = 4096;
+constexpr size_t kStaticPartialFloats = 1u << 20;
+constexpr size_t kStaticScratchBytes = kStaticTickets * sizeof(int) + kStaticPartialFloats * sizeof(float);
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[kStaticScratchBytes];
+
+static unsigned char *g_static_base[64];  // per device, filled on the first call there
+
+void set_last_error(const char *msg);  // megakernel.cu: text for mk_last_error
+
+static cudaError_t static_scratch(int **tickets_out, float **partial_out) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (!g_static_base[device]) {
+        unsigned char *ptr = nullptr;
+        e = cudaGetSymbolAddress((void **)&ptr, g_gemv_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_base[device] = ptr;
+    }
+    *tickets_out = reinterpret_cast<int *>(g_static_base[device]);
+    *partial_out = reinterpret_cast<float *>(g_static_base[device] + kStaticTickets * sizeof(int));
+    return cudaSuccess;
+}
+
 }  // namespace mk
+
+extern "C" int mk_gemv_static(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y,
+                              int32_t m, int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream) {
+    using namespace mk;
+    if (!x || !y || m <= 0 || k <= 0 || (k % 256) != 0 || batch < 1 || batch > kGemvMaxBatch ||
+        (is_packed ? (!packed || !scales) : !w_bf16)) {
+        set_last_error("mk_gemv_static: null pointer, batch outside 1..8, or k not a multiple of 256");
+        return MK_ERR_BAD_ARGUMENT;
+    }
+    const int row_blocks = (m + kGemvRows - 1) / kGemvRows;
+    const int chunks = (k + kGemvChunk - 1) / kGemvChunk;
+    int *tickets = nullptr;
+    float *partial = nullptr;
+    if (chunks > 1) {
+        if (row_blocks > kStaticTickets || (size_t)chunks * kGemvMaxBatch * (size_t)m > kStaticPartialFloats) {
+            char msg[256];
+            snprintf(msg, sizeof(msg),
+                     "mk_gemv_static: m=%d k=%d needs %d tickets and %zu partial floats; the fixed scratch holds %d and %zu "
+                     "(use mk_gemv for larger problems)",
+                     m, k, row_blocks, (size_t)chunks * kGemvMaxBatch * (size_t)m, kStaticTickets, kStaticPartialFloats);
+            set_last_error(msg);
+            return MK_ERR_UNSUPPORTED;
+        }
+        cudaError_t e = static_scratch(&tickets, &partial);
+        if (e != cudaSuccess) {
+            set_last_error("mk_gemv_static: cudaGetSymbolAddress of the fixed scratch failed (first call made during stream capture?)");
+            return (int)e;
+        }
+        // the tickets count arrivals per row block and must start at zero; the partial sums are written before they are read
+        e = cudaMemsetAsync(tickets, 0, row_blocks * sizeof(int), (cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const dim3 grid(row_blocks * chunks), block(kGemvWarps * 32);
+    if (is_packed)
+        gemv_mma_kernel<true><<<grid, block, 0, (cudaStream_t)stream>>>(nullptr, (const uint8_t *)packed, (const uint8_t *)scales,
+                                                                        (const bf16 *)x, (bf16 *)y, m, k, tensor_scale, batch,
+                                                                        chunks, partial, tickets);
+    else
+        gemv_mma_kernel<false><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16 *)w_bf16, nullptr, nullptr, (const bf16 *)x,
+                                                                         (bf16 *)y, m, k, 1.0f, batch, chunks, partial, tickets);
+    return (int)cudaGetLastError();
+}

@@ -1431,6 +1431,9 @@ static int cuda_fail(cudaError_t e, const char *what) {
     return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
 }
 
+// lets the library's other translation units leave a message for mk_last_error
+void set_last_error(const char *msg) { snprintf(g_error, sizeof(g_error), "%s", msg); }
+
 struct Handle {
     MkModelDesc desc;
     Params params;
