@@ -202,6 +202,9 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
 /* Tuning knobs without a counterpart in the reference (its equivalents are
  * compile-time constants, include/config.cuh:7-72). */
 #define MK_OPT_WAIT_BUDGET_CYCLES 0  /* same as mk_set_wait_budget */
+#define MK_OPT_MAX_INFLIGHT_TILES 2  /* weight tiles (64 KiB bf16 / 18 KiB NVFP4) one loader keeps in flight */
+#define MK_OPT_EARLY_POLL_SHIFT   1  /* consumers stop watching a dependency counter and poll the data cells
+                                      * themselves once it is within target >> shift of its target; 31 = never */
 int mk_set_option(void *handle, int32_t option, int64_t value);
 
 void mk_destroy(void *handle);

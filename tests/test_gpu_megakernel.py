@@ -246,6 +246,7 @@ def test_bounded_wait_reports_status_instead_of_hanging(tiny):
     kernel returns, the status words say which worker/opcode/slot gave up, and
     the handle keeps working afterwards."""
     from thor_megakernels_b200.demos.latency.instructions import O_ProjResidual
+    from thor_megakernels_b200._lib import MK_OPT_EARLY_POLL_SHIFT
     from thor_megakernels_b200.runtime import Megakernel, MegakernelError
     from thor_megakernels_b200.scheduler import tensorize_instructions
     from types import SimpleNamespace
@@ -263,7 +264,16 @@ def test_bounded_wait_reports_status_instead_of_hanging(tiny):
     with pytest.raises(MegakernelError) as err:
         mk.status()
     st = err.value.status
+    # default: consumers poll the tagged data cells themselves -> code 5 (data never arrived)
+    assert (st["code"], st["worker"], st["opcode"], st["slot"]) == (5, 0, 4, 0)
+    # with early polling off they watch the dependency counter first -> code 1 with its value and target
+    mk.set_option(MK_OPT_EARLY_POLL_SHIFT, 31)
+    mk.step(0)
+    with pytest.raises(MegakernelError) as err:
+        mk.status()
+    st = err.value.status
     assert (st["code"], st["worker"], st["opcode"], st["slot"], st["detail"], st["expected"]) == (1, 0, 4, 0, 0, 32)
+    mk.set_option(MK_OPT_EARLY_POLL_SHIFT, 0)
     # the same handle runs a full step afterwards
     mk.set_wait_budget(4_000_000_000)
     mk.set_schedule(g.instructions, g.timings)
@@ -410,13 +420,13 @@ def test_llama8b_shapes_two_layers():
         got = mk_gen.run(torch.tensor([[token]], device="cuda"), pos_id=pos)
         torch.cuda.synchronize()
         for name in ("post_ln_rope_q", "attn_out", "silu_out", "hidden_states", "logits"):
-            assert_parity(name, getattr(sched.globs, name), getattr(cpu_sched.globs, name), getattr(exact_sched.globs, name))
+            assert_parity(name, getattr(sched.globs, name), getattr(cpu_sched.globs, name), getattr(exact_sched.globs, name), layers=2)
         assert torch.equal(sched.globs.barriers.cpu()[:, :6], cpu_sched.globs.barriers[:, :6])
         # layer 0's appended rows see no accumulated rounding noise
         assert_close("k row", model.stacked_kv_cache[0][0, 0, pos], cpu_model.stacked_kv_cache[0][0, 0, pos])
         assert_close("v row", model.stacked_kv_cache[1][0, 0, pos], cpu_model.stacked_kv_cache[1][0, 0, pos])
         assert_parity("k rows", model.stacked_kv_cache[0][:, 0, pos], cpu_model.stacked_kv_cache[0][:, 0, pos],
-                      cpu_exact.stacked_kv_cache[0][:, 0, pos])
+                      cpu_exact.stacked_kv_cache[0][:, 0, pos], layers=2)
         if int(got) != int(want):
             top2 = torch.topk(cpu_sched.globs.logits.float(), 2).values
             assert float(top2[0] - top2[1]) <= 0.125

@@ -22,6 +22,8 @@ MK_STEP_WRITE_TOKEN = 4
 MK_STEP_TIMINGS = 8
 
 MK_OPT_WAIT_BUDGET_CYCLES = 0
+MK_OPT_EARLY_POLL_SHIFT = 1
+MK_OPT_MAX_INFLIGHT_TILES = 2
 
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1

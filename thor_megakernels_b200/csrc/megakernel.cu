@@ -75,6 +75,8 @@ constexpr int kTimingSlots = 128;
 constexpr int kConsumerBarrier = 1;                       // named barrier id
 constexpr int kSliceCounterRow = 7;                       // barriers[layer, 7, slice]: gate/up blocks done per 2048-column slice
 constexpr int kMaxDownSlices = 8;                         // intermediate_size <= 16384
+constexpr int kDownGroup = 4;     // row blocks whose slices the merging storer fetches together
+constexpr int kFetchPerLane = 6;  // cells per lane in that fetch
 constexpr int kTaggedPartials = 32;                       // attention slices per KV head the scratch can hold
 
 // timing slots (reference include/util.cuh:225-256)
@@ -98,6 +100,8 @@ struct Params {
     unsigned flags;
     float attn_scale, eps;
     long long spin_cycles;
+    int max_inflight;  // weight tiles a loader keeps in flight
+    int early_shift;  // consumers start polling cells once a counter is within expected >> early_shift of its target (31: never early)
     int down_slices;  // inter / 2048
     int down_total;   // (hidden / 16) * down_slices
     // weights
@@ -146,6 +150,7 @@ struct __align__(128) Smem {
     float partial[kPartialBufs][kConsumerWarps][kBlockRows];
     float red[2][kConsumerWarps];
     __align__(16) bf16 xbuf[2 * kChunkCols];  // normalised activations, re-read in the MMA operand layout
+    float down_parts[kDownGroup][kMaxDownSlices][kBlockRows];  // down-projection slices of the blocks being merged
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
     uint64_t pfull[kPartialBufs];
@@ -466,7 +471,8 @@ template <int NCH, bool FP4>
 __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
     using F = Fmt<FP4>;
     const uint64_t policy = l2_evict_first_policy();
-    Ring<F::stages> ring;
+    Ring<F::stages> ring, land;  // next stage to fill / oldest fill not yet known to have landed
+    int outstanding = 0;
     uint32_t live = 0;  // stages whose most recent fill was actually issued
     TileCursor<NCH, FP4> tiles;
     Tile t;
@@ -477,7 +483,17 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
             stamp(p, t.slot, kEvLoaderStart, t_start);
             last_slot = t.slot;
         }
+        // Keep at most `max_inflight` tiles outstanding: more than the memory system
+        // needs to stay busy only lengthens its queues, and with them the latency of
+        // the small loads on the dependency path between SMs.
+        while (outstanding > 0 && mbar_try_wait(&s.full[land.stage], land.phase)) { land.advance(); --outstanding; }
+        while (outstanding >= p.max_inflight && !aborted(s)) {
+            wait_mbar(p, s, &s.full[land.stage], land.phase, kFailRing, t.opcode, t.slot, (int)land.stage);
+            land.advance();
+            --outstanding;
+        }
         wait_mbar(p, s, &s.empty[ring.stage], ring.phase ^ 1u, kFailRing, t.opcode, t.slot, (int)ring.stage);
+        ++outstanding;
         if (aborted(s)) {
             live &= ~(1u << ring.stage);
         } else {
@@ -540,7 +556,9 @@ struct ConsumerState {
 // All consumer threads block until `ctr >= expected` (polled by one thread).
 __device__ __forceinline__ void consumer_wait(const Params &p, Smem &s, int ctid, const int *ctr, int expected,
                                               int opcode, int slot) {
-    if (ctid == 0) wait_counter(p, s, ctr, expected, opcode, slot);
+    // The counter is a hint: once most producers are done, the threads go on to
+    // poll the cells they need, which saves the counter's round trip for the last ones.
+    if (ctid == 0) wait_counter(p, s, ctr, expected - (expected >> p.early_shift), opcode, slot);
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
 }
 
@@ -795,20 +813,16 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, uint32_t t
         if (t < t1 && t < p.pos) load_row(kq[j], vq[j], t);
     }
 
-    if (ctid == 0) {
-        stamp(p, slot, kEvAtWait, t_start);
-        for (int i = 0; i < kGroup; ++i)
-            wait_counter(p, s, counter(p, layer, 0, kv_head * kGroup + i), blocks_per_head, 2, slot);
-        wait_counter(p, s, counter(p, layer, 0, p.hq + kv_head), blocks_per_head, 2, slot);
-        wait_counter(p, s, counter(p, layer, 0, p.hq + p.hkv + kv_head), blocks_per_head, 2, slot);
-        stamp(p, slot, kEvDoneWait, t_start);
-    }
-    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
+    // No counter wait: Q and the new K/V row arrive in tagged cells, and each
+    // thread waits on exactly the cells it reads (one L2 round trip after the
+    // producer's store instead of counter poll + load).
+    if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
 
     uint4 q[V];
     const unsigned long long *q_cells = p.t_q + ((size_t)layer * p.hq * D + (size_t)(kv_head * kGroup + h) * D + d0) / 2;
 #pragma unroll
     for (int v = 0; v < V; ++v) load8_wait(p, s, q_cells + 4 * v, tag, q[v], 2, slot);
+    if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
     // the row appended by this launch, if it is one of those fetched early
 #pragma unroll
     for (int j = 0; j < kDepth; ++j) {
@@ -945,12 +959,8 @@ __device__ void attention_reduction(const Params &p, Smem &s, int ctid, uint32_t
     const int terminal = __ldg(ins + 4), n = __ldg(ins + 5);
     const int out_slot = __ldg(ins + 6 + n);
     const int D = p.hd;
-    if (ctid == 0) {
-        stamp(p, slot, kEvAtWait, t_start);
-        for (int h = 0; h < kGroup; ++h) wait_counter(p, s, counter(p, layer, 1, head0 + h), num_partials, 3, slot);
-        stamp(p, slot, kEvDoneWait, t_start);
-    }
-    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
+    // partials arrive in tagged cells: every thread waits on the cells it reads
+    if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
     for (int idx = ctid; idx < kGroup * D; idx += kConsumerThreads) {
         const int h = idx / D, d = idx % D;
         const int head = head0 + h;
@@ -1267,43 +1277,81 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // so no ordering between the slice producers is needed.
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
             const bool owner = red == p.down_slices - 1;
-            for (int b = b0; b < b1; ++b) {
-                const float y = collect_block(p, s, st, lane, op, slot);
-                const int row = b * kBlockRows + (lane & 15);
-                unsigned long long *parts = p.t_down + ((size_t)layer * p.down_slices) * p.hidden + row;
-                if (writer && !aborted(s)) st_tagged(parts + (size_t)red * p.hidden, __float_as_uint(y), tag);
+            unsigned long long *slice0 = p.t_down + ((size_t)layer * p.down_slices) * p.hidden;
+            // The owner fetches the other slices of up to `group` row blocks with all
+            // loads in flight at once (kFetchPerLane cells per lane) and retries the
+            // whole set until every cell carries this launch's tag: one L2 round trip
+            // after the last producer's store, however many blocks the instruction has.
+            const int group = owner && red > 0 ? max(1, min(kDownGroup, (32 * kFetchPerLane) / (kBlockRows * red))) : kDownGroup;
+            for (int c0 = b0; c0 < b1; c0 += group) {
+                const int nb = min(group, b1 - c0);
+                for (int i = 0; i < nb; ++i) {
+                    const float y = collect_block(p, s, st, lane, op, slot);
+                    const int row = (c0 + i) * kBlockRows + (lane & 15);
+                    if (writer && !aborted(s)) st_tagged(slice0 + (size_t)red * p.hidden + row, __float_as_uint(y), tag);
+                    if (writer) s.down_parts[i][red][lane] = y;
+                }
                 if (!owner) continue;
-                float h = 0.f;
-                if (writer) {
-                    // one attempt on everything at once, then wait for what is missing
-                    const unsigned long long *rcell = p.t_resid + ((size_t)layer * p.hidden + row) / 2;
-                    unsigned long long rv = ld_tagged1(rcell);
-                    unsigned long long pv[kMaxDownSlices];
+                if (lane == 0) stamp(p, slot, 55, t_start);  // own slices parked
+                const int ncell = nb * red * kBlockRows;
+                unsigned long long pv[kFetchPerLane], rv[kDownGroup];
+                Deadline dl = start_deadline();
+                while (true) {
+                    bool ok = true;
 #pragma unroll
-                    for (int sl = 0; sl < kMaxDownSlices; ++sl)
-                        if (sl < red) pv[sl] = ld_tagged1(parts + (size_t)sl * p.hidden);
-                    uint32_t pr = tag_payload(rv);
-                    if (!tag_ok(rv, tag)) pr = load1_wait(p, s, rcell, tag, op, slot);
-                    h = (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
-                    float total = 0.f;
+                    for (int j = 0; j < kFetchPerLane; ++j) {
+                        const int idx = lane + 32 * j;
+                        if (idx < ncell) {
+                            const int i = idx / (red * kBlockRows), rem = idx - i * red * kBlockRows;
+                            pv[j] = ld_tagged1(slice0 + (size_t)(rem >> 4) * p.hidden + (c0 + i) * kBlockRows + (rem & 15));
+                        }
+                    }
 #pragma unroll
-                    for (int sl = 0; sl < kMaxDownSlices; ++sl) {
-                        if (sl <= red) {
-                            float part = y;
-                            if (sl < red) {
-                                uint32_t bits = tag_payload(pv[sl]);
-                                if (!tag_ok(pv[sl], tag)) bits = load1_wait(p, s, parts + (size_t)sl * p.hidden, tag, op, slot);
-                                part = __uint_as_float(bits);
-                            }
+                    for (int i = 0; i < kDownGroup; ++i)
+                        if (i < nb && pair_writer)
+                            rv[i] = ld_tagged1(p.t_resid + ((size_t)layer * p.hidden + (c0 + i) * kBlockRows + lane) / 2);
+#pragma unroll
+                    for (int j = 0; j < kFetchPerLane; ++j)
+                        if (lane + 32 * j < ncell) ok &= tag_ok(pv[j], tag);
+#pragma unroll
+                    for (int i = 0; i < kDownGroup; ++i)
+                        if (i < nb && pair_writer) ok &= tag_ok(rv[i], tag);
+                    if (__all_sync(0xffffffffu, ok) || !keep_waiting(p, s, dl, op, slot, 3)) break;
+                }
+                if (lane == 0) {
+                    stamp(p, slot, 56, t_start);  // other slices present
+                    if (p.flags & MK_STEP_TIMINGS) p.timings[((size_t)blockIdx.x * p.queue_len + slot) * kTimingSlots + 57] = (int)dl.it;
+                }
+#pragma unroll
+                for (int j = 0; j < kFetchPerLane; ++j) {
+                    const int idx = lane + 32 * j;
+                    if (idx < ncell) {
+                        const int i = idx / (red * kBlockRows), rem = idx - i * red * kBlockRows;
+                        s.down_parts[i][rem >> 4][rem & 15] = __uint_as_float(tag_payload(pv[j]));
+                    }
+                }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < kDownGroup; ++i) {
+                    if (i >= nb) break;
+                    // residual pair (rows lane, lane+1) is held by the even lane
+                    const uint32_t pr = __shfl_sync(0xffffffffu, tag_payload(rv[i]), lane & ~1);
+                    float h = (lane & 1) ? bf16_hi(pr) : bf16_lo(pr);
+                    if (writer) {
+                        float total = 0.f;
+                        for (int sl = 0; sl <= red; ++sl) {
+                            const float part = s.down_parts[i][sl][lane];
                             if (p.model_numerics) total += part;
                             else h = round_bf16(h + round_bf16(part));
                         }
+                        if (p.model_numerics) h = round_bf16(h + round_bf16(total * down_scale(p, layer)));
                     }
-                    if (p.model_numerics) h = round_bf16(h + round_bf16(total * down_scale(p, layer)));
+                    const float h_next = __shfl_xor_sync(0xffffffffu, h, 1);
+                    if (pair_writer && !aborted(s))
+                        st_tagged(p.t_hidden + ((size_t)layer * p.hidden + (c0 + i) * kBlockRows + lane) / 2,
+                                  pack_bf16x2(h, h_next), tag);
                 }
-                const float h_next = __shfl_xor_sync(0xffffffffu, h, 1);
-                if (pair_writer && !aborted(s))
-                    st_tagged(p.t_hidden + ((size_t)layer * p.hidden + row) / 2, pack_bf16x2(h, h_next), tag);
+                __syncwarp();
             }
             publish(p, s, lane, counter(p, layer, 5, 0), b1 - b0);
             break;
@@ -1582,6 +1630,8 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.skip_attn_reduction = d->skip_attn_reduction;
     p.attn_scale = d->attn_scale; p.eps = d->rms_norm_eps;
     p.spin_cycles = 4000000000ll;
+    p.early_shift = 0;
+    p.max_inflight = kMaxStages;
     p.down_slices = slices;
     p.down_total = (H / kBlockRows) * slices;
     p.qkv_w = (const bf16 *)d->qkv_w; p.attn_norm_w = (const bf16 *)d->attn_norm_w; p.o_w = (const bf16 *)d->o_w;
@@ -1728,6 +1778,14 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     case MK_OPT_WAIT_BUDGET_CYCLES:
         if (value <= 0) return fail(MK_ERR_BAD_ARGUMENT, "wait budget must be positive");
         h->params.spin_cycles = value;
+        return 0;
+    case MK_OPT_MAX_INFLIGHT_TILES:
+        if (value < 1) return fail(MK_ERR_BAD_ARGUMENT, "at least one tile must be in flight");
+        h->params.max_inflight = (int)(value > kMaxStages ? kMaxStages : value);
+        return 0;
+    case MK_OPT_EARLY_POLL_SHIFT:
+        if (value < 0 || value > 31) return fail(MK_ERR_BAD_ARGUMENT, "early-poll shift must be 0..31");
+        h->params.early_shift = (int)value;
         return 0;
     default:
         return fail(MK_ERR_BAD_ARGUMENT, "mk_set_option: unknown option %d", option);
