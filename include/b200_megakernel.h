@@ -207,6 +207,28 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
                                       * themselves once it is within target >> shift of its target; 31 = never */
 int mk_set_option(void *handle, int32_t option, int64_t value);
 
+/*
+ * Tensor parallelism over the GPUs of one node, one process per GPU.  The
+ * reference shards only its PyTorch model (megakernels/llama.py:192-207,
+ * 308-310, 665-691: q/k/v/up/gate by rows, o/down by columns, heads and FFN
+ * divided by tp_size); here the handle of rank r is created on that shard
+ * (num_q_heads, num_kv_heads, intermediate_size, vocab_size are the rank's 1/n
+ * shares, lm_head_w its rows, embed_w the full table) and the two all-reduces per
+ * layer run inside the kernel: every rank stores its partial sums into every
+ * GPU's exchange buffer over NVLink peer memory and adds what it received in
+ * rank order (bit-identical on all ranks).  MK_STEP_WRITE_TOKEN merges the
+ * ranks' greedy candidates the same way; token ids are global.
+ *
+ *   mk_tp_init    allocates this GPU's exchange buffer and returns its CUDA IPC
+ *                 handle (MK_TP_HANDLE_BYTES bytes) for the host to all-gather;
+ *   mk_tp_connect takes the world's handles in rank order and maps the peers.
+ *
+ * Every rank must then make the same sequence of mk_step calls.
+ */
+#define MK_TP_HANDLE_BYTES 64
+int mk_tp_init(void *handle, int32_t rank, int32_t world, int32_t vocab_offset, void *ipc_handle_out);
+int mk_tp_connect(void *handle, const void *ipc_handles);
+
 void mk_destroy(void *handle);
 
 /*

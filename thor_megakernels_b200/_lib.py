@@ -21,6 +21,7 @@ MK_STEP_RESET_BARRIERS = 2
 MK_STEP_WRITE_TOKEN = 4
 MK_STEP_TIMINGS = 8
 
+MK_TP_HANDLE_BYTES = 64
 MK_OPT_WAIT_BUDGET_CYCLES = 0
 MK_OPT_EARLY_POLL_SHIFT = 1
 MK_OPT_MAX_INFLIGHT_TILES = 2
@@ -31,7 +32,7 @@ MK_WEIGHTS_NVFP4 = 1
 EXPORTED_SYMBOLS = [
     "mk_last_error", "mk_create", "mk_set_schedule", "mk_step", "mk_query", "mk_status",
     "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
-    "mk_gemv_static",
+    "mk_gemv_static", "mk_tp_init", "mk_tp_connect",
 ]
 
 
@@ -108,6 +109,8 @@ def load() -> C.CDLL:
     lib.mk_nvfp4_quantize.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
     lib.mk_gemv.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
     lib.mk_gemv_static.argtypes = lib.mk_gemv.argtypes
+    lib.mk_tp_init.argtypes = [vp, i32, i32, i32, vp]
+    lib.mk_tp_connect.argtypes = [vp, vp]
     lib.mk_abi_sizeof.argtypes = [i32]
     lib.mk_set_option.argtypes = [vp, i32, C.c_int64]
     for name in EXPORTED_SYMBOLS:

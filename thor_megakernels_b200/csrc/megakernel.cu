@@ -77,6 +77,7 @@ constexpr int kSliceCounterRow = 7;                       // barriers[layer, 7, 
 constexpr int kMaxDownSlices = 8;                         // intermediate_size <= 16384
 constexpr int kDownGroup = 4;     // row blocks whose slices the merging storer fetches together
 constexpr int kFetchPerLane = 6;  // cells per lane in that fetch
+constexpr int kMaxRanks = 8;                              // tensor-parallel ranks
 constexpr int kTaggedPartials = 32;                       // attention slices per KV head the scratch can hold
 
 // timing slots (reference include/util.cuh:225-256)
@@ -102,7 +103,9 @@ struct Params {
     long long spin_cycles;
     int max_inflight;  // weight tiles a loader keeps in flight
     int early_shift;  // consumers start polling cells once a counter is within expected >> early_shift of its target (31: never early)
-    int down_slices;  // inter / 2048
+    int o_cols, o_chunks, o_width;  // output projection: input columns (Hq*D), tiles per row block, columns per tile
+    int down_width;   // columns of one down-projection slice (multiple of 256, at most 2048)
+    int down_slices;  // inter / down_width
     int down_total;   // (hidden / 16) * down_slices
     // weights
     const bf16 *qkv_w, *attn_norm_w, *o_w, *mlp_norm_w, *up_w, *gate_w, *down_w, *lm_norm_w, *lm_w, *embed_w;
@@ -136,6 +139,12 @@ struct Params {
     unsigned long long *t_silu;     // [L][inter/2]
     unsigned long long *t_oi;       // [L][hq][kTaggedPartials][hd] one fp32 per cell: attention partial outputs
     unsigned long long *t_lse;      // [L][hq][kTaggedPartials]     one fp32 per cell
+    // Tensor parallelism: this rank's shapes above are its 1/n share; the partial
+    // output-projection and down-projection sums of all ranks meet in exchange
+    // buffers, one per GPU, that every rank can write (peer-mapped).
+    int tp_rank, tp_world;          // tp_world == 1: no exchange
+    int vocab_offset;               // global id of this rank's first vocabulary row
+    unsigned long long *xchg[kMaxRanks];  // [rank] -> that GPU's exchange buffer (own entry = local memory)
     unsigned *epoch;                // launch tag, advanced by the last CTA of every launch
     unsigned long long *argmax_key;
     int *done_counter;
@@ -335,6 +344,22 @@ __device__ __forceinline__ int *counter(const Params &p, int layer, int row, int
     return p.bar + ((size_t)layer * p.bar_rows + row) * p.bar_cols + col;
 }
 
+// Exchange buffer of a GPU, in 8-byte tagged cells (one fp32 each):
+//   [parity 2][which 2][layer][source rank][hidden]   partial sums (which 0: output projection, 1: down projection)
+//   [parity 2][source rank][2]                        greedy-token candidates (logit bits, inverted global index)
+// Parity = launch tag & 1: a rank can run at most one launch ahead of its peers
+// (it needs their partials of the same launch to get through layer 0), so two
+// copies keep a fast rank from overwriting cells a slow one still reads.
+__device__ __forceinline__ size_t xchg_partial_cells(const Params &p) {
+    return (size_t)2 * 2 * p.layers * p.tp_world * p.hidden;
+}
+__device__ __forceinline__ unsigned long long *xchg_partials(const Params &p, int gpu, uint32_t tag, int which, int layer) {
+    return p.xchg[gpu] + ((((size_t)(tag & 1u) * 2 + which) * p.layers + layer) * p.tp_world) * p.hidden;
+}
+__device__ __forceinline__ unsigned long long *xchg_token(const Params &p, int gpu, uint32_t tag, int source) {
+    return p.xchg[gpu] + xchg_partial_cells(p) + ((size_t)(tag & 1u) * p.tp_world + source) * 2;
+}
+
 __device__ __forceinline__ const int *instruction_at(const Params &p, int slot) {
     return p.instructions + ((size_t)blockIdx.x * p.queue_len + slot) * kInstrWords;
 }
@@ -364,6 +389,7 @@ struct Tile {
     size_t stride_bytes;
     const uint8_t *scales;
     size_t scale_stride;
+    int width;  // columns of this tile (multiple of 256, at most 2048)
     int opcode;
     int slot;
 };
@@ -381,7 +407,8 @@ struct TileCursor {
     // bf16: element pointers; NVFP4: code / scale byte pointers (second pair = gate matrix of op 5)
     const uint8_t *base = nullptr, *base2 = nullptr, *sbase = nullptr, *sbase2 = nullptr;
     size_t row_elems = 0;   // K of the matrix
-    size_t col0 = 0;        // first column (down projection: the instruction's 2048-column slice)
+    size_t col0 = 0;        // first column (down projection: the instruction's column slice)
+    int width = kChunkCols; // columns per tile
 
     __device__ __forceinline__ void bind(const bf16 *w, const MkNvfp4Matrix *q, size_t layer, size_t layer_elems,
                                          bool second) {
@@ -400,7 +427,7 @@ struct TileCursor {
             if (idx < cnt) {
                 const int block = (op == 5) ? __ldg(ins + 3 + idx) : first_block + idx;
                 const bool second = op == 5 && sub >= NCH;
-                const size_t col = col0 + (size_t)((op == 6) ? 0 : (sub % NCH)) * kChunkCols;
+                const size_t col = col0 + (size_t)((op == 6) ? 0 : (op == 4 ? sub : sub % NCH)) * kChunkCols;
                 const size_t elem = (size_t)block * kBlockRows * row_elems + col;
                 if constexpr (FP4) {
                     t.src = (second ? base2 : base) + elem / 2;
@@ -413,6 +440,7 @@ struct TileCursor {
                     t.scales = nullptr;
                     t.scale_stride = 0;
                 }
+                t.width = width;
                 t.opcode = op;
                 t.slot = slot;
                 if (++sub == nsub) { sub = 0; ++idx; }
@@ -421,7 +449,7 @@ struct TileCursor {
             if (++slot >= p.queue_len) return false;
             ins = instruction_at(p, slot);
             op = __ldg(ins);
-            idx = 0; sub = 0; cnt = 0; nsub = NCH; col0 = 0;
+            idx = 0; sub = 0; cnt = 0; nsub = NCH; col0 = 0; width = kChunkCols;
             const size_t hidden = p.hidden;
             switch (op) {
             case 1: {
@@ -434,7 +462,8 @@ struct TileCursor {
             case 4: {
                 const int layer = __ldg(ins + 1);
                 first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block;
-                row_elems = (size_t)p.hq * p.hd;
+                row_elems = (size_t)p.o_cols;
+                nsub = p.o_chunks; width = p.o_width;
                 bind(p.o_w, p.q_o, layer, hidden * row_elems, false);
                 break;
             }
@@ -450,7 +479,8 @@ struct TileCursor {
                 const int layer = __ldg(ins + 1);
                 first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block; nsub = 1;
                 row_elems = p.inter;
-                col0 = (size_t)__ldg(ins + 4) * kChunkCols;
+                width = p.down_width;
+                col0 = (size_t)__ldg(ins + 4) * width;
                 bind(p.down_w, p.q_down, layer, hidden * row_elems, false);
                 break;
             }
@@ -499,25 +529,26 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
         } else {
             live |= 1u << ring.stage;
             uint64_t *bar = &s.full[ring.stage];
-            mbar_arrive_expect_tx(bar, F::tile_tx);
+            const uint32_t code_row = t.width / 2, scale_row = t.width / 16, row_bytes = t.width * 2;
+            mbar_arrive_expect_tx(bar, FP4 ? kBlockRows * (code_row + scale_row) : kBlockRows * row_bytes);
             uint8_t *dst = s.ring + ring.stage * F::stage_bytes;
             if constexpr (FP4) {
                 // rows of a K=2048 matrix are contiguous: one copy each for codes and scales
-                if (t.stride_bytes == (size_t)kFp4CodeRow) {
+                if (t.width == kChunkCols && t.stride_bytes == (size_t)kFp4CodeRow) {
                     bulk_load(dst, t.src, kBlockRows * kFp4CodeRow, bar, policy);
                     bulk_load(dst + kFp4ScaleOffset, t.scales, kBlockRows * kFp4ScaleRow, bar, policy);
                 } else {
 #pragma unroll 4
                     for (int r = 0; r < kBlockRows; ++r) {
-                        bulk_load(dst + r * kFp4CodeRow, t.src + r * t.stride_bytes, kFp4CodeRow, bar, policy);
-                        bulk_load(dst + kFp4ScaleOffset + r * kFp4ScaleRow, t.scales + r * t.scale_stride, kFp4ScaleRow,
+                        bulk_load(dst + r * kFp4CodeRow, t.src + r * t.stride_bytes, code_row, bar, policy);
+                        bulk_load(dst + kFp4ScaleOffset + r * kFp4ScaleRow, t.scales + r * t.scale_stride, scale_row,
                                   bar, policy);
                     }
                 }
             } else {
 #pragma unroll 4
                 for (int r = 0; r < kBlockRows; ++r)
-                    bulk_load(dst + r * kRowPitch, t.src + r * t.stride_bytes, kRowBytes, bar, policy);
+                    bulk_load(dst + r * kRowPitch, t.src + r * t.stride_bytes, row_bytes, bar, policy);
             }
         }
         ring.advance();
@@ -671,13 +702,16 @@ __device__ __forceinline__ void load_normed(const Params &p, Smem &s, int ctid, 
 // previous reads of xbuf and this call (their dependency wait does).
 template <int NCH, bool FP4>
 __device__ __forceinline__ void load_operand(const Params &p, Smem &s, const unsigned long long *cells, uint32_t tag,
-                                             int ctid, uint4 (&x)[NCH][8], int opcode, int slot) {
+                                             int ctid, int ncols, uint4 (&x)[NCH][8], int opcode, int slot) {
     const int cw = ctid >> 5, t = ctid & 3;
     uint4 mine[NCH];
     uint32_t missing = 0;
 #pragma unroll
-    for (int c = 0; c < NCH; ++c)
-        if (!try_load8(cells + (c * kChunkCols + ctid * 8) / 2, tag, mine[c])) missing |= 1u << c;
+    for (int c = 0; c < NCH; ++c) {
+        mine[c] = make_uint4(0u, 0u, 0u, 0u);  // columns beyond the vector count as zero
+        if (c * kChunkCols + ctid * 8 < ncols && !try_load8(cells + (c * kChunkCols + ctid * 8) / 2, tag, mine[c]))
+            missing |= 1u << c;
+    }
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
         if (missing & (1u << c)) load8_wait(p, s, cells + (c * kChunkCols + ctid * 8) / 2, tag, mine[c], opcode, slot);
@@ -699,14 +733,18 @@ __device__ __forceinline__ void load_operand(const Params &p, Smem &s, const uns
 // conversion is needed.  The per-warp results (16 rows) go to the storer.
 template <int NCH, bool FP4>
 __device__ __forceinline__ void consume_block(const Params &p, Smem &s, ConsumerState<FP4> &st, int lane, int cw,
-                                              const uint4 (&x)[NCH][8], int opcode, int slot) {
+                                              const uint4 (&x)[NCH][8], int opcode, int slot, int nchunks = NCH,
+                                              int width = kChunkCols) {
     float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
     const int g = lane >> 2, t = lane & 3;
+    const bool in_tile = cw * 256 < width;  // narrower tiles leave the upper warps without columns
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
+        if (c >= nchunks) break;
         wait_mbar(p, s, &s.full[st.ring.stage], st.ring.phase, kFailRing, opcode, slot, (int)st.ring.stage);
         const uint8_t *tile = s.ring + st.ring.stage * Fmt<FP4>::stage_bytes;
-        if constexpr (FP4) {
+        if (!in_tile) {
+        } else if constexpr (FP4) {
             // 32 code bytes and 4 scale bytes per row: columns cw*256 + t*64 .. +63
             const uint8_t *cg = tile + g * kFp4CodeRow + cw * 128 + t * 32;
             const uint8_t *ch = cg + 8 * kFp4CodeRow;
@@ -1045,9 +1083,9 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, layer, 2, 0), p.hq, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-            load_operand<NCH, FP4>(p, s, p.t_attn + (size_t)layer * (p.hq * p.hd / 2), tag, ctid, x, op, slot);
+            load_operand<NCH, FP4>(p, s, p.t_attn + (size_t)layer * (p.o_cols / 2), tag, ctid, p.o_cols, x, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
-            for (int b = b0; b < b1; ++b) consume_block<NCH, FP4>(p, s, st, lane, cw, x, op, slot);
+            for (int b = b0; b < b1; ++b) consume_block<NCH, FP4>(p, s, st, lane, cw, x, op, slot, p.o_chunks, p.o_width);
             break;
         }
         case 5: {
@@ -1068,12 +1106,13 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             // only the gate/up rows of this 2048-column slice have to be ready
-            consumer_wait(p, s, ctid, counter(p, layer, kSliceCounterRow, red), kChunkCols / kBlockRows, op, slot);
+            consumer_wait(p, s, ctid, counter(p, layer, kSliceCounterRow, red), p.down_width / kBlockRows, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
             uint4 xs[1][8];
-            load_operand<1, FP4>(p, s, p.t_silu + ((size_t)layer * p.inter + (size_t)red * kChunkCols) / 2, tag, ctid, xs, op, slot);
+            load_operand<1, FP4>(p, s, p.t_silu + ((size_t)layer * p.inter + (size_t)red * p.down_width) / 2, tag, ctid,
+                                 p.down_width, xs, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
-            for (int b = b0; b < b1; ++b) consume_block<1, FP4>(p, s, st, lane, cw, xs, op, slot);
+            for (int b = b0; b < b1; ++b) consume_block<1, FP4>(p, s, st, lane, cw, xs, op, slot, 1, p.down_width);
             break;
         }
         case 7: {
@@ -1135,6 +1174,58 @@ __device__ __forceinline__ unsigned long long argmax_key(float logit_bf16, int i
     uint32_t bits = __float_as_uint(logit_bf16) >> 16;
     bits = (bits & 0x8000u) ? (~bits & 0xffffu) : (bits | 0x8000u);
     return ((unsigned long long)bits << 32) | (unsigned long long)(0xffffffffu - (uint32_t)index);
+}
+
+// Tensor-parallel all-reduce of a [hidden] vector of fp32 partial sums, issued
+// from inside the step: every rank stores its partial of a row into the exchange
+// buffer of every GPU (its own included) as a tagged cell, over NVLink for the
+// peers; then every rank adds the partials it received in rank order, so all
+// ranks compute bit-identical sums without any flag or barrier between GPUs.
+__device__ __forceinline__ void tp_push(const Params &p, uint32_t tag, int which, int layer, int row, float v) {
+    for (int r = 0; r < p.tp_world; ++r)
+        st_tagged_sys(xchg_partials(p, r, tag, which, layer) + (size_t)p.tp_rank * p.hidden + row, __float_as_uint(v), tag);
+}
+
+// Receiving side for row blocks [b0, b1): two blocks at a time (lane = block
+// parity x row), all ranks' cells in flight at once and retried as a set until
+// every tag matches; then residual + bf16(sum) goes to `out` as residual-stream
+// cells.  The residual comes from `plain` (layer-0 input) or from `resid` cells.
+__device__ void tp_fold_blocks(const Params &p, Smem &s, int lane, uint32_t tag, int which, int layer, int b0, int b1,
+                               const bf16 *plain, const unsigned long long *resid, unsigned long long *out, int op,
+                               int slot) {
+    const unsigned long long *mine = xchg_partials(p, p.tp_rank, tag, which, layer);
+    for (int c0 = b0; c0 < b1; c0 += 2) {
+        const int b = c0 + (lane >> 4);
+        const bool valid = b < b1;
+        const int row = (valid ? b : c0) * kBlockRows + (lane & 15);
+        unsigned long long v[kMaxRanks];
+        unsigned long long rv = 0ull;
+        Deadline dl = start_deadline();
+        while (true) {
+            bool ok = true;
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r) {
+                v[r] = 0ull;
+                if (valid && r < p.tp_world) v[r] = ld_tagged1_sys(mine + (size_t)r * p.hidden + row);
+            }
+            if (valid && plain == nullptr) rv = ld_tagged1(resid + row / 2);
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (valid && r < p.tp_world) ok &= tag_ok(v[r], tag);
+            if (valid && plain == nullptr) ok &= tag_ok(rv, tag);
+            if (__all_sync(0xffffffffu, ok) || !keep_waiting(p, s, dl, op, slot, 4)) break;
+        }
+        float total = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < p.tp_world) total += __uint_as_float(tag_payload(v[r]));
+        float h;
+        if (plain != nullptr) h = ldcg_bf16(plain + row);
+        else h = (row & 1) ? bf16_hi(tag_payload(rv)) : bf16_lo(tag_payload(rv));
+        const float o = round_bf16(h + round_bf16(total));
+        const float o_next = __shfl_xor_sync(0xffffffffu, o, 1);
+        if (valid && (lane & 1) == 0 && !aborted(s)) st_tagged(out + row / 2, pack_bf16x2(o, o_next), tag);
+    }
 }
 
 template <int NCH>
@@ -1225,6 +1316,18 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                 return (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
             };
             const float ts = matrix_scale(p.q_o, layer);
+            if (p.tp_world > 1) {
+                // this rank's columns of the projection are a partial sum: all-reduce, then the residual add
+                for (int b = b0; b < b1; ++b) {
+                    const float y = collect_block(p, s, st, lane, op, slot) * ts;
+                    if (writer && !aborted(s)) tp_push(p, tag, 0, layer, b * kBlockRows + lane, y);
+                }
+                tp_fold_blocks(p, s, lane, tag, 0, layer, b0, b1, layer == 0 ? step_input : nullptr,
+                               p.t_hidden + (size_t)(layer > 0 ? layer - 1 : 0) * (p.hidden / 2),
+                               p.t_resid + (size_t)layer * (p.hidden / 2), op, slot);
+                publish(p, s, lane, counter(p, layer, 3, 0), b1 - b0);
+                break;
+            }
             float h = writer ? residual(b0 * kBlockRows + lane) : 0.f;
             for (int b = b0; b < b1; ++b) {
                 const float y = round_bf16(collect_block(p, s, st, lane, op, slot) * ts);
@@ -1257,7 +1360,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             }
             // per 2048-column slice of the product (what one down-projection
             // instruction reads), then the reference interpreter's single counter
-            const int my_slice = lane < n ? (__ldg(ins + 3 + lane) * kBlockRows) / kChunkCols : -1;
+            const int my_slice = lane < n ? (__ldg(ins + 3 + lane) * kBlockRows) / p.down_width : -1;
             __syncwarp();
             for (int sl = 0; sl < p.down_slices; ++sl) {
                 const int cnt = __popc(__ballot_sync(0xffffffffu, my_slice == sl));
@@ -1334,6 +1437,15 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
 #pragma unroll
                 for (int i = 0; i < kDownGroup; ++i) {
                     if (i >= nb) break;
+                    if (p.tp_world > 1) {
+                        // the local slices are a partial sum over this rank's columns: send it to every rank
+                        if (writer && !aborted(s)) {
+                            float total = 0.f;
+                            for (int sl = 0; sl <= red; ++sl) total += s.down_parts[i][sl][lane];
+                            tp_push(p, tag, 1, layer, (c0 + i) * kBlockRows + lane, total * down_scale(p, layer));
+                        }
+                        continue;
+                    }
                     // residual pair (rows lane, lane+1) is held by the even lane
                     const uint32_t pr = __shfl_sync(0xffffffffu, tag_payload(rv[i]), lane & ~1);
                     float h = (lane & 1) ? bf16_hi(pr) : bf16_lo(pr);
@@ -1353,6 +1465,9 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                 }
                 __syncwarp();
             }
+            if (owner && p.tp_world > 1)
+                tp_fold_blocks(p, s, lane, tag, 1, layer, b0, b1, nullptr, p.t_resid + (size_t)layer * (p.hidden / 2),
+                               p.t_hidden + (size_t)layer * (p.hidden / 2), op, slot);
             publish(p, s, lane, counter(p, layer, 5, 0), b1 - b0);
             break;
         }
@@ -1448,7 +1563,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const Params p
     }
     if (tid == 0) *p.epoch = (tag + 1u == 0u) ? 1u : tag + 1u;  // the next launch accepts none of this one's cells
     if (tid == 0) {
-        const unsigned long long key = __ldcg(p.argmax_key);
+        unsigned long long key = __ldcg(p.argmax_key);
+        if (p.tp_world > 1 && (p.flags & MK_STEP_WRITE_TOKEN)) {
+            // Vocabulary is sharded: send this rank's best (logit bits, global id) to every
+            // rank, wait for everybody's, keep the largest key (lowest id on ties).
+            if (key) key = (key & 0xffffffff00000000ull) | (unsigned long long)((uint32_t)(key & 0xffffffffull) - (uint32_t)p.vocab_offset);
+            for (int r = 0; r < p.tp_world; ++r) {
+                unsigned long long *dst = xchg_token(p, r, tag, p.tp_rank);
+                st_tagged_sys(dst, (uint32_t)(key >> 32), tag);
+                st_tagged_sys(dst + 1, (uint32_t)key, tag);
+            }
+            unsigned long long best = 0ull;
+            Deadline dl = start_deadline();
+            for (int r = 0; r < p.tp_world; ++r) {
+                const unsigned long long *src = xchg_token(p, p.tp_rank, tag, r);
+                unsigned long long hi = ld_tagged1_sys(src), lo = ld_tagged1_sys(src + 1);
+                while (!(tag_ok(hi, tag) && tag_ok(lo, tag)) && keep_waiting(p, s, dl, 7, 0, 5)) {
+                    hi = ld_tagged1_sys(src);
+                    lo = ld_tagged1_sys(src + 1);
+                }
+                const unsigned long long k = ((unsigned long long)tag_payload(hi) << 32) | tag_payload(lo);
+                if (k > best) best = k;
+            }
+            key = best;
+        }
         if ((p.flags & MK_STEP_WRITE_TOKEN) && p.token_out != nullptr)
             *p.token_out = key ? (int)(0xffffffffu - (uint32_t)(key & 0xffffffffull)) : 0;
         *p.argmax_key = 0ull;
@@ -1494,6 +1632,11 @@ struct Handle {
     size_t smem_bytes = 0;
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
+    // tensor parallelism
+    void *xchg = nullptr;              // this GPU's exchange buffer (cudaMalloc, exported over CUDA IPC)
+    size_t xchg_bytes = 0;
+    int tp_world_pending = 0;          // set by mk_tp_init, becomes params.tp_world in mk_tp_connect
+    void *peer_xchg[kMaxRanks] = {};   // peers' buffers opened over CUDA IPC
 };
 
 static const void *kernel_for(int nch, bool fp4) {
@@ -1534,11 +1677,20 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
         return fail(MK_ERR_BAD_ARGUMENT, "mk_create: non-positive dimension");
     if (H != kChunkCols && H != 2 * kChunkCols)
         return fail(MK_ERR_UNSUPPORTED, "hidden_size %d: kernel streams 2048-column tiles, hidden must be 2048 or 4096", H);
-    if (d->num_q_heads * D != H) return fail(MK_ERR_UNSUPPORTED, "num_q_heads*head_dim (%d) must equal hidden_size (%d)", d->num_q_heads * D, H);
+    // Input width of the output projection: hidden_size for a whole model, a 1/n
+    // share of it for a tensor-parallel rank.
+    const int o_cols = d->num_q_heads * D;
+    if (o_cols > H || (o_cols >= kChunkCols ? o_cols % kChunkCols != 0 : o_cols % 256 != 0))
+        return fail(MK_ERR_UNSUPPORTED, "num_q_heads*head_dim = %d: must be a multiple of 2048 up to hidden_size, or a multiple of 256 below 2048", o_cols);
     if (D != 64 && D != 128) return fail(MK_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", D);
     if (d->num_q_heads != kGroup * d->num_kv_heads)
         return fail(MK_ERR_UNSUPPORTED, "query group size must be %d (got %d q heads, %d kv heads)", kGroup, d->num_q_heads, d->num_kv_heads);
-    if (d->intermediate_size % kChunkCols) return fail(MK_ERR_UNSUPPORTED, "intermediate_size %d not a multiple of 2048", d->intermediate_size);
+    // Down-projection column slices: the widest multiple of 256 up to 2048 that divides
+    // intermediate_size (2048 for whole models; e.g. 1792 for 14336/2, /4 and /8).
+    int down_width = 0;
+    for (int w = kChunkCols; w >= 256; w -= 256)
+        if (d->intermediate_size % w == 0) { down_width = w; break; }
+    if (!down_width) return fail(MK_ERR_UNSUPPORTED, "intermediate_size %d not a multiple of 256", d->intermediate_size);
     if (d->vocab_size % kBlockRows) return fail(MK_ERR_UNSUPPORTED, "vocab_size %d not a multiple of 16", d->vocab_size);
     if (d->barrier_rows < 8 || d->barrier_cols < d->num_q_heads + 2 * d->num_kv_heads)
         return fail(MK_ERR_BAD_ARGUMENT, "barriers tensor too small: rows %d cols %d", d->barrier_rows, d->barrier_cols);
@@ -1601,7 +1753,7 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     if (h->resident < 1) { delete h; return fail(MK_ERR_RESIDENCY, "kernel cannot keep one CTA resident per SM"); }
 
     // scratch: tagged cells | argmax key (8 B) | exit counter | status[8] | launch tag
-    const int slices = d->intermediate_size / kChunkCols;
+    const int slices = d->intermediate_size / down_width;
     if (slices > kMaxDownSlices) { delete h; return fail(MK_ERR_UNSUPPORTED, "intermediate_size %d: at most %d column slices", d->intermediate_size, kMaxDownSlices); }
     const size_t L = d->num_layers, qd = (size_t)d->num_q_heads * D, kvd = (size_t)d->num_kv_heads * D;
     const size_t n_resid = L * H / 2, n_hidden = L * H / 2, n_down = L * slices * H, n_q = L * qd / 2, n_kv = L * kvd / 2, n_attn = L * qd / 2;
@@ -1632,6 +1784,10 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.spin_cycles = 4000000000ll;
     p.early_shift = 0;
     p.max_inflight = kMaxStages;
+    p.o_cols = o_cols;
+    p.o_chunks = o_cols >= kChunkCols ? o_cols / kChunkCols : 1;
+    p.o_width = o_cols >= kChunkCols ? kChunkCols : o_cols;
+    p.down_width = down_width;
     p.down_slices = slices;
     p.down_total = (H / kBlockRows) * slices;
     p.qkv_w = (const bf16 *)d->qkv_w; p.attn_norm_w = (const bf16 *)d->attn_norm_w; p.o_w = (const bf16 *)d->o_w;
@@ -1661,6 +1817,7 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.status = (int *)(sc + cell_bytes + 32);
     p.epoch = (unsigned *)(sc + cell_bytes + 64);
     p.model_numerics = fp4 ? 1 : 0;
+    p.tp_rank = 0; p.tp_world = 1; p.vocab_offset = 0;
     if (fp4) {
         MkNvfp4Matrix *dev = (MkNvfp4Matrix *)(sc + cell_bytes + 256);
         const MkNvfp4Matrix *src[] = {d->qkv_q, d->o_q, d->up_q, d->gate_q, d->down_q};
@@ -1792,9 +1949,63 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     }
 }
 
+extern "C" int mk_tp_init(void *handle, int32_t rank, int32_t world, int32_t vocab_offset, void *ipc_handle_out) {
+    Handle *h = (Handle *)handle;
+    if (!h || !ipc_handle_out) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_init: null argument");
+    if (world < 2 || world > kMaxRanks || rank < 0 || rank >= world || vocab_offset < 0)
+        return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_init: rank %d of %d (2..%d ranks), vocabulary offset %d", rank, world, kMaxRanks, vocab_offset);
+    if (h->xchg) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_init: already initialised");
+    static_assert(sizeof(cudaIpcMemHandle_t) == MK_TP_HANDLE_BYTES, "IPC handle size");
+    const Params &p = h->params;
+    const size_t cells = (size_t)2 * 2 * p.layers * world * p.hidden + (size_t)2 * world * 2;
+    h->xchg_bytes = cells * sizeof(unsigned long long);
+    cudaError_t e = cudaSetDevice(h->device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    e = cudaMalloc(&h->xchg, h->xchg_bytes);
+    if (e != cudaSuccess) { h->xchg = nullptr; return cuda_fail(e, "cudaMalloc(exchange buffer)"); }
+    e = cudaMemset(h->xchg, 0, h->xchg_bytes);  // tag 0 is never a launch tag
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle((cudaIpcMemHandle_t *)ipc_handle_out, h->xchg);
+    if (e != cudaSuccess) { cudaFree(h->xchg); h->xchg = nullptr; return cuda_fail(e, "exchange buffer set-up"); }
+    h->params.tp_rank = rank;
+    h->params.vocab_offset = vocab_offset;
+    h->tp_world_pending = world;
+    return 0;
+}
+
+extern "C" int mk_tp_connect(void *handle, const void *ipc_handles) {
+    Handle *h = (Handle *)handle;
+    if (!h || !ipc_handles) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_connect: null argument");
+    if (!h->xchg || h->tp_world_pending < 2) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_connect: call mk_tp_init first");
+    if (h->params.tp_world > 1) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_connect: already connected");
+    cudaError_t e = cudaSetDevice(h->device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    const cudaIpcMemHandle_t *handles = (const cudaIpcMemHandle_t *)ipc_handles;
+    for (int r = 0; r < h->tp_world_pending; ++r) {
+        if (r == h->params.tp_rank) {
+            h->params.xchg[r] = (unsigned long long *)h->xchg;
+            continue;
+        }
+        void *ptr = nullptr;
+        e = cudaIpcOpenMemHandle(&ptr, handles[r], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle (are all ranks on one NVLink-connected node, one process per GPU?)");
+        h->peer_xchg[r] = ptr;
+        h->params.xchg[r] = (unsigned long long *)ptr;
+    }
+    // every rank starts counting launches from the same tag
+    const unsigned first_tag = 1;
+    e = cudaMemcpy(h->params.epoch, &first_tag, sizeof(first_tag), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(launch tag)");
+    h->params.tp_world = h->tp_world_pending;
+    return 0;
+}
+
 extern "C" void mk_destroy(void *handle) {
     Handle *h = (Handle *)handle;
     if (!h) return;
+    for (int r = 0; r < kMaxRanks; ++r)
+        if (h->peer_xchg[r]) cudaIpcCloseMemHandle(h->peer_xchg[r]);
+    if (h->xchg) cudaFree(h->xchg);
     cudaFree(h->scratch);
     delete h;
 }

@@ -136,6 +136,18 @@ __device__ __forceinline__ unsigned long long ld_tagged1(const unsigned long lon
     return v;
 }
 
+// System-scope variants for cells that another GPU writes over NVLink.
+__device__ __forceinline__ void st_tagged_sys(unsigned long long *cell, uint32_t payload, uint32_t tag) {
+    const unsigned long long v = ((unsigned long long)tag << 32) | payload;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(cell), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long ld_tagged1_sys(const unsigned long long *cell) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(cell) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ bool tag_ok(unsigned long long v, uint32_t tag) { return (uint32_t)(v >> 32) == tag; }
 __device__ __forceinline__ uint32_t tag_payload(unsigned long long v) { return (uint32_t)v; }
 

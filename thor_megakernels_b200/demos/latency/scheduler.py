@@ -92,7 +92,7 @@ def make_globals(model, skip_attn_reduction: bool = True, num_attention_partitio
         down_proj_block_size=16,
         o_proj_block_size=16,
         lm_head_block_size=16,
-        matvec_reduction_size=2048,
+        matvec_reduction_size=down_slice_width(cfg.intermediate_size),
         qkv_block_size=16,
         attn_kv_block_size=16,
         attn_reduction_size=4,
@@ -101,10 +101,23 @@ def make_globals(model, skip_attn_reduction: bool = True, num_attention_partitio
     return globs
 
 
+def down_slice_width(intermediate_size: int) -> int:
+    """Columns of one down-projection slice: 2048 (the reference's
+    ``matvec_reduction_size``) when it divides ``intermediate_size``, else the
+    widest multiple of 256 below it that does (a tensor-parallel share of the
+    FFN, e.g. 1792 for 14336/2).  The kernel applies the same rule."""
+    for width in range(2048, 0, -256):
+        if intermediate_size % width == 0:
+            return width
+    raise ValueError(f"intermediate_size {intermediate_size} is not a multiple of 256")
+
+
 def _even_ranges(num_blocks: int, workers: int):
-    """Contiguous block ranges whose sizes differ by at most one."""
+    """Contiguous block ranges whose sizes differ by at most one.  With fewer
+    blocks than workers (small tensor-parallel shares) every block is its own range."""
     per = num_blocks / workers
-    assert per > 1
+    if per <= 1:
+        return [(b, b + 1) for b in range(num_blocks)]
     return [(round(w * per), round((w + 1) * per)) for w in range(workers)]
 
 
@@ -120,10 +133,9 @@ def schedule_qkv(globs: Globals, layer_idx: int):
 def schedule_upgate(globs: Globals, layer_idx: int):
     blocks = assert_div(globs.intermediate_size, globs.up_gate_proj_block_size)
     workers = globs.sm_count()
-    assert blocks / workers > 1
     room = INTS_PER_INSTRUCTION - 3  # opcode, layer and list length take three words
     out = []
-    for w in range(workers):
+    for w in range(min(workers, blocks)):
         mine = list(range(w, blocks, workers))
         for i in range(0, len(mine), room):
             out.append(LayerNormDoubleMatVecSiLU(layer_idx, mine[i : i + room]))
@@ -143,8 +155,9 @@ def schedule_downproj(globs: Globals, layer_idx: int):
     out = []
     taken = 0
     for w in range(workers):
-        share = (len(jobs) - taken) / (workers - w)
-        assert share > 1
+        if taken == len(jobs):
+            break
+        share = max(1.0, (len(jobs) - taken) / (workers - w))
         chunk = jobs[taken : taken + round(share)]
         col = chunk[0][0]
         chunk = [j for j in chunk if j[0] == col]

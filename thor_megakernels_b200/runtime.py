@@ -207,6 +207,23 @@ class Megakernel:
             raise err
         return out
 
+    # -- tensor parallelism ------------------------------------------------
+    def tp_init(self, rank: int, world: int, vocab_offset: int) -> bytes:
+        """Allocates this GPU's exchange buffer; returns its CUDA IPC handle (64
+        bytes) for the caller to all-gather across the ranks."""
+        buf = C.create_string_buffer(_lib.MK_TP_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_tp_init(self.handle, int(rank), int(world), int(vocab_offset), buf))
+        return bytes(buf.raw)
+
+    def tp_connect(self, handles: list[bytes]):
+        """Maps the peers' exchange buffers; ``handles`` in rank order."""
+        if any(len(h) != _lib.MK_TP_HANDLE_BYTES for h in handles):
+            raise ValueError("every IPC handle must be 64 bytes")
+        blob = C.create_string_buffer(b"".join(handles), len(handles) * _lib.MK_TP_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_tp_connect(self.handle, blob))
+
     def set_wait_budget(self, cycles: int):
         _lib.check(self.lib.mk_set_wait_budget(self.handle, int(cycles)))
 
