@@ -18,7 +18,14 @@ synthetic weights N(0, 0.02), synthetic prompt/KV).  The JSON line reports
                  interpreter) timed on this box's cores over a few tokens.
 
 ``--impl reference`` times only that CPU interpreter (one token per step).
-With N > 1 (under torchrun) every rank decodes an independent replica.
+With N > 1 (under torchrun) every rank decodes an independent replica of that
+workload (weak scaling: a 1B model at batch 1 gains nothing from being split).
+
+``--workload llama8b-tp`` (or ``llama1b-tp``) instead splits ONE sequence's
+model over the N GPUs (tensor parallel, all-reduces inside the kernel over
+NVLink peer memory; strong scaling; N = 1 runs the whole model on one GPU):
+Llama-3.1-8B architecture, bf16, batch 1, 8192 cached positions, 64 tokens per
+step.
 """
 from __future__ import annotations
 
@@ -43,6 +50,17 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without
 
 MODEL = dict(hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
              intermediate_size=8192, vocab_size=128256)
+
+
+MODEL_8B = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=14336, vocab_size=128256, tie_word_embeddings=False,
+                rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=8192))
+TP_WORKLOADS = {
+    # name: (model, cached positions, tokens per step, seed)
+    "llama8b-tp": (MODEL_8B, 8192, 64, 4),
+    "llama1b-tp": (MODEL, PROMPT_LEN, TOKENS_PER_REQUEST, 0),
+}
 
 
 def linear_weight_bytes(cfg: dict) -> int:
@@ -348,6 +366,119 @@ def run_ours(args, rank, world, local):
         print(json.dumps(line), flush=True)
 
 
+def run_tp(args, rank, world, local):
+    """One sequence, model split over the ranks; world == 1 runs the whole model."""
+    from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder, pick_num_attention_partitions
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+    from thor_megakernels_b200.runtime import Megakernel
+    from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+    from thor_megakernels_b200.tp import TensorParallelDecoder
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py measures the CUDA megakernel; no CUDA device is visible")
+    cfg, ctx, ntok, seed = TP_WORKLOADS[args.workload]
+    if args.self_test:
+        cfg = dict(cfg, num_hidden_layers=2, vocab_size=4096)
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    extra = ExtraModelConfig(interleave_rope=True, max_len_override=ctx + ntok + 8)
+    # the device generator draws the same stream on every GPU, so all ranks hold the same model
+    model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=seed, device=device, generate_on=device)
+    gen = torch.Generator(device=device).manual_seed(3)
+    for cache in model.stacked_kv_cache:
+        cache[:, :, :ctx] = torch.randn(cache[:, :, :ctx].shape, generator=gen, device=device).bfloat16()
+    partitions = pick_num_attention_partitions(ctx, ntok) if ctx >= 512 else 1
+    if world > 1:
+        dec = TensorParallelDecoder(model, rank, world, num_attention_partitions=partitions)
+        mk = dec.mk
+    else:
+        sched = LatencyScheduleBuilder.build(model, skip_attn_reduction=partitions == 1, num_attention_partitions=partitions)
+        tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+        mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data)
+        sched.globs.barriers.zero_()
+    stream = torch.cuda.current_stream(device)
+    first = torch.tensor([17], dtype=torch.int32, device=device)
+    produced = torch.zeros(ntok, dtype=torch.int32, device=device)
+
+    def request():
+        mk.decode(first, produced, start_pos=ctx, count=ntok, stream=stream)
+
+    for _ in range(max(args.warmup, 3)):
+        request()
+    torch.cuda.synchronize(device)
+    mk.status()
+    sampler = ClockSampler(local)
+    barrier(world)
+    torch.cuda.synchronize(device)
+    sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(args.steps):
+        request()
+    end.record(stream)
+    torch.cuda.synchronize(device)
+    barrier(world)
+    clocks = sampler.stop()
+    mk.status()
+    elapsed_ms = max_over_ranks(start.elapsed_time(end), world)
+    launches = args.steps * ntok
+
+    host_first = torch.tensor([17], dtype=torch.int32).pin_memory()
+    host_out = torch.zeros(ntok, dtype=torch.int32).pin_memory()
+
+    def request_e2e():
+        first.copy_(host_first, non_blocking=True)
+        mk.decode(first, produced, start_pos=ctx, count=ntok, stream=stream)
+        host_out.copy_(produced, non_blocking=True)
+        stream.synchronize()
+
+    for _ in range(2):
+        request_e2e()
+    barrier(world)
+    torch.cuda.synchronize(device)
+    start.record(stream)
+    for _ in range(args.steps):
+        request_e2e()
+    end.record(stream)
+    torch.cuda.synchronize(device)
+    e2e_ms = max_over_ranks(start.elapsed_time(end), world)
+    tokens = torch.zeros(world * ntok, dtype=torch.int32, device=device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_gather_into_tensor(tokens, produced)
+        assert all(torch.equal(tokens[r * ntok:(r + 1) * ntok], produced) for r in range(world)), "ranks produced different tokens"
+    if rank == 0:
+        peak, peak_src = measured_hbm_peak()
+        kv = kv_bytes_per_position(cfg)
+        total_bytes = sum(linear_weight_bytes(cfg) + kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
+        launch_ms = elapsed_ms / launches
+        achieved = total_bytes / world / (launch_ms / 1000.0) / 1e9  # per GPU: every rank streams 1/world of the bytes
+        line = {
+            "metric": "decode_tokens_per_s", "value": launches / (elapsed_ms / 1000.0), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": f"{args.workload}: {'SELF-TEST 2-layer ' if args.self_test else ''}batch-1 greedy decode, "
+                            f"{ctx} cached positions, {ntok} tokens per step",
+                "step": f"{ntok} megakernel launches per rank",
+                "ms_per_token": launch_ms,
+                "parallelism": f"tp{world}" if world > 1 else "single",
+                "attention_partitions_per_kv_head": partitions,
+                "l2": "inputs larger than L2",
+            },
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": total_bytes / world,
+                         "launch_ms": launch_ms, "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "note": "per GPU: total algorithmic bytes / n_gpus over the launch time"},
+            "e2e": {"value": launches / (e2e_ms / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": 4,
+                    "d2h_bytes_per_step": 4 * ntok, "api": "Megakernel.decode on every rank", "ms_per_token": e2e_ms / launches},
+            "gpu_launches": launches, "clocks": clocks, "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one megakernel launch from an ncu capture
 # of this workload at position 60 (summarised under profiles/).
 MEASURED_DRAM_TRAFFIC_PER_LAUNCH = 2_475_626_000 + 8_757_248
@@ -361,6 +492,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tokens", type=int, default=4, help="decode tokens timed for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="llama1b", choices=["llama1b", *TP_WORKLOADS],
+                    help="llama1b: the headline workload (replicas when N > 1); *-tp: one sequence split over the GPUs")
     ap.add_argument("--self-test", action="store_true",
                     help="2-layer, 4096-token-vocabulary model to exercise this script quickly; not a benchmark")
     args = ap.parse_args()
@@ -370,6 +503,8 @@ def main():
     try:
         if args.impl == "reference":
             run_reference(args, rank, world)
+        elif args.workload != "llama1b":
+            run_tp(args, rank, world, local)
         else:
             run_ours(args, rank, world, local)
     finally:
