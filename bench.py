@@ -388,7 +388,11 @@ def run_tp(args, rank, world, local):
     gen = torch.Generator(device=device).manual_seed(3)
     for cache in model.stacked_kv_cache:
         cache[:, :, :ctx] = torch.randn(cache[:, :, :ctx].shape, generator=gen, device=device).bfloat16()
-    partitions = pick_num_attention_partitions(ctx, ntok) if ctx >= 512 else 1
+    # split the cache of every KV head into as many slices as there are SMs to take them (at most 24 per
+    # head, at least 256 positions each), so that one wave of attention instructions covers the GPU
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    kv_heads_here = cfg["num_key_value_heads"] // world
+    partitions = min(pick_num_attention_partitions(ctx, ntok), max(1, sms // kv_heads_here)) if ctx >= 512 else 1
     if world > 1:
         dec = TensorParallelDecoder(model, rank, world, num_attention_partitions=partitions)
         mk = dec.mk

@@ -851,6 +851,21 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, uint32_t t
         if (t < t1 && t < p.pos) load_row(kq[j], vq[j], t);
     }
 
+    // The rest of a long slice is pulled into L2 now, also before the producers
+    // are done: the loop below holds only kDepth rows per warp in registers, too few
+    // bytes in flight to cover DRAM latency, but enough to cover an L2 hit.
+    {
+        const int first = t0 + kDepth * kConsumerWarps, last = min(t1, p.pos);
+        const int lines_per_row = D / 64;  // 128-byte lines of one head's K (or V) row
+        const bf16 *krow0 = kbase - d0, *vrow0 = vbase - d0;
+        const int items = (last - first) * lines_per_row * 2;
+        for (int it = ctid; it < items; it += kConsumerThreads) {
+            const int row = first + it / (2 * lines_per_row), rem = it % (2 * lines_per_row);
+            const bf16 *src = ((rem & 1) ? vrow0 : krow0) + (size_t)row * tok_stride + (rem >> 1) * 64;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+        }
+    }
+
     // No counter wait: Q and the new K/V row arrive in tagged cells, and each
     // thread waits on exactly the cells it reads (one L2 round trip after the
     // producer's store instead of counter poll + load).
@@ -999,20 +1014,38 @@ __device__ void attention_reduction(const Params &p, Smem &s, int ctid, uint32_t
     const int D = p.hd;
     // partials arrive in tagged cells: every thread waits on the cells it reads
     if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
+    // The log-sum-exps of the 4 heads' partials go through shared memory (one cell
+    // per thread, all in flight together) instead of being re-read by every thread.
+    float *lse_s = &s.attn[0][0][0];  // [kGroup][kTaggedPartials]
+    if (ctid < kGroup * n) {
+        const int h = ctid / n, j = ctid % n;
+        const unsigned long long *cell = p.t_lse + ((size_t)layer * p.hq + head0 + h) * kTaggedPartials + __ldg(ins + 6 + j);
+        lse_s[h * kTaggedPartials + j] = __uint_as_float(load1_wait(p, s, cell, tag, 3, slot));
+    }
+    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
     for (int idx = ctid; idx < kGroup * D; idx += kConsumerThreads) {
         const int h = idx / D, d = idx % D;
         const int head = head0 + h;
-        const unsigned long long *lse = p.t_lse + ((size_t)layer * p.hq + head) * kTaggedPartials;
         const unsigned long long *oi = p.t_oi + (((size_t)layer * p.hq + head) * kTaggedPartials) * D + d;
         float mx = -INFINITY;
-        for (int j = 0; j < n; ++j)
-            mx = fmaxf(mx, __uint_as_float(load1_wait(p, s, lse + __ldg(ins + 6 + j), tag, 3, slot)));
+        for (int j = 0; j < n; ++j) mx = fmaxf(mx, lse_s[h * kTaggedPartials + j]);
         float denom = 0.f, num = 0.f;
-        for (int j = 0; j < n; ++j) {
-            const int src = __ldg(ins + 6 + j);
-            const float f = exp2f(__uint_as_float(load1_wait(p, s, lse + src, tag, 3, slot)) - mx);
-            denom += f;
-            num = fmaf(__uint_as_float(load1_wait(p, s, oi + (size_t)src * D, tag, 3, slot)), f, num);
+        // partial outputs: eight independent loads in flight, validated afterwards
+        for (int j0 = 0; j0 < n; j0 += 8) {
+            unsigned long long raw[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (j0 + u < n) raw[u] = ld_tagged1(oi + (size_t)__ldg(ins + 6 + j0 + u) * D);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (j0 + u < n) {
+                    uint32_t bits = tag_payload(raw[u]);
+                    if (!tag_ok(raw[u], tag)) bits = load1_wait(p, s, oi + (size_t)__ldg(ins + 6 + j0 + u) * D, tag, 3, slot);
+                    const float f = exp2f(lse_s[h * kTaggedPartials + j0 + u] - mx);
+                    denom += f;
+                    num = fmaf(__uint_as_float(bits), f, num);
+                }
+            }
         }
         const float out = num / denom;
         const float out_bf = round_bf16(out);
