@@ -25,7 +25,9 @@ workload (weak scaling: a 1B model at batch 1 gains nothing from being split).
 model over the N GPUs (tensor parallel, all-reduces inside the kernel over
 NVLink peer memory; strong scaling; N = 1 runs the whole model on one GPU):
 Llama-3.1-8B architecture, bf16, batch 1, 8192 cached positions, 64 tokens per
-step.
+step.  ``--workload gemv`` times the single-operator GEMV (bf16 and NVFP4
+weights, batch 1 and 4); ``--workload llama1b-nvfp4-4k`` the NVFP4 weight-only
+megakernel against bf16 weights at 4096 cached positions.
 """
 from __future__ import annotations
 
@@ -366,6 +368,142 @@ def run_ours(args, rank, world, local):
         print(json.dumps(line), flush=True)
 
 
+def run_gemv(args, rank, world, local):
+    """Single-operator GEMV (bf16 and NVFP4 weight-only, batch 1 and 4) at the two
+    shapes of the 1B FFN.  A call streams 9-34 MB, less than L2 holds, so every
+    call uses the next of enough independently quantised weight copies to exceed
+    L2 (~300 MB per case): each weight byte comes from HBM.  128 calls are
+    captured in one CUDA graph so that launch latency (about the kernel's own
+    duration) stays out of the figure."""
+    if rank != 0:
+        return
+    from thor_megakernels_b200 import nvfp4
+
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    peak, peak_src = measured_hbm_peak()
+    gen = torch.Generator(device=device).manual_seed(2)
+    calls = 128
+    results = []
+    for m, k in ((8192, 2048), (2048, 8192)):
+        for fmt in ("nvfp4", "bf16"):
+            per_weight = 0.5625 if fmt == "nvfp4" else 2.0
+            copies = max(2, int(300e6 / (m * k * per_weight)) + 1)
+            weights = []
+            for _ in range(copies):
+                w = (torch.randn(m, k, device=device, generator=gen) * 0.02).bfloat16()
+                weights.append(nvfp4.quantize_weight(w) if fmt == "nvfp4" else w)
+            for batch in (1, 4):
+                x = torch.randn(batch, k, device=device, generator=gen).bfloat16()
+                y = torch.empty(batch, m, dtype=torch.bfloat16, device=device)
+                nvfp4.gemv(weights[0], x, out=y)  # first call outside capture (allocates the split-K scratch)
+                torch.cuda.synchronize(device)
+                stream = torch.cuda.Stream(device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(stream):
+                    for i in range(3):
+                        nvfp4.gemv(weights[i % copies], x, out=y)
+                    stream.synchronize()
+                    with torch.cuda.graph(graph, stream=stream):
+                        for i in range(calls):
+                            nvfp4.gemv(weights[i % copies], x, out=y)
+                    for _ in range(max(args.warmup, 3)):
+                        graph.replay()
+                    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record(stream)
+                    for _ in range(args.steps):
+                        graph.replay()
+                    end.record(stream)
+                    stream.synchronize()
+                us = 1000.0 * start.elapsed_time(end) / (args.steps * calls)
+                weight_bytes = m * k * per_weight
+                gbs = weight_bytes / (us * 1e-6) / 1e9
+                results.append({"m": m, "k": k, "weights": fmt, "batch": batch, "us_per_call": us, "GB/s": gbs,
+                                "frac_of_measured_peak": gbs / peak, "weight_copies_cycled": copies})
+    best = max(results, key=lambda r: r["GB/s"])
+    line = {
+        "metric": "gemv_weight_GBps", "value": best["GB/s"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 activations, NVFP4 or bf16 weights", "data": "synthetic",
+        "config": {"workload": "single-operator GEMV, shapes 8192x2048 and 2048x8192, batch 1 and 4",
+                   "l2": "weight copies cycled so that every call reads from HBM (footprint ~300 MB per case > 126 MB L2)",
+                   "timing": f"{calls} calls per CUDA graph replay, CUDA events around {args.steps} replays"},
+        "roofline": {"bound": "hbm", "achieved": best["GB/s"], "peak": peak, "unit": "GB/s", "frac": best["GB/s"] / peak,
+                     "traffic": None, "peak_source": peak_src},
+        "cases": results, "gpu_launches": args.steps * calls * len(results), "cpu_baseline": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_long_context(args, rank, world, local):
+    """Llama-3.2-1B architecture with 4096 cached positions, 256 tokens per step:
+    NVFP4 weight-only against bf16 weights on the same schedule (one GPU)."""
+    if rank != 0:
+        return
+    from thor_megakernels_b200 import nvfp4
+    from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder, pick_num_attention_partitions
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+    from thor_megakernels_b200.runtime import Megakernel
+    from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    cfg = dict(MODEL)
+    ctx, ntok = 4096, 256
+    extra = ExtraModelConfig(interleave_rope=True, max_len_override=ctx + ntok + 8)
+    model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=0, device=device, generate_on=device)
+    gen = torch.Generator(device=device).manual_seed(3)
+    for cache in model.stacked_kv_cache:
+        cache[:, :, :ctx] = torch.randn(cache[:, :, :ctx].shape, generator=gen, device=device).bfloat16()
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    partitions = min(pick_num_attention_partitions(ctx, ntok), max(1, sms // cfg["num_key_value_heads"]))
+    sched = LatencyScheduleBuilder.build(model, skip_attn_reduction=False, num_attention_partitions=partitions)
+    tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+    peak, peak_src = measured_hbm_peak()
+    kv = kv_bytes_per_position(cfg)
+    kv_bytes = sum(kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
+    stream = torch.cuda.current_stream(device)
+    first = torch.tensor([17], dtype=torch.int32, device=device)
+    produced = torch.zeros(ntok, dtype=torch.int32, device=device)
+    out = {}
+    for fmt in ("bf16", "nvfp4"):
+        quantized = nvfp4.quantize_model(model) if fmt == "nvfp4" else None
+        mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
+        sched.globs.barriers.zero_()
+        for _ in range(max(args.warmup, 3)):
+            mk.decode(first, produced, start_pos=ctx, count=ntok, stream=stream)
+        torch.cuda.synchronize(device)
+        mk.status()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(args.steps):
+            mk.decode(first, produced, start_pos=ctx, count=ntok, stream=stream)
+        end.record(stream)
+        torch.cuda.synchronize(device)
+        mk.status()
+        ms = start.elapsed_time(end) / (args.steps * ntok)
+        weights = linear_weight_bytes(cfg) * (0.5625 / 2.0 if fmt == "nvfp4" else 1.0)
+        gbs = (weights + kv_bytes) / (ms * 1e-3) / 1e9
+        out[fmt] = {"ms_per_token": ms, "tokens_per_s": 1000.0 / ms, "algorithmic_bytes_per_launch": weights + kv_bytes,
+                    "GB/s": gbs, "frac_of_measured_peak": gbs / peak}
+        mk.close()
+    line = {
+        "metric": "decode_tokens_per_s", "value": out["nvfp4"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": out["nvfp4"]["ms_per_token"] * ntok,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations and KV, NVFP4 weights",
+        "data": "synthetic",
+        "config": {"workload": f"llama-3.2-1b-arch, every linear NVFP4 weight-only, {ctx} cached positions, {ntok} tokens per step",
+                   "attention_partitions_per_kv_head": partitions, "l2": "inputs larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": out["nvfp4"]["GB/s"], "peak": peak, "unit": "GB/s",
+                     "frac": out["nvfp4"]["GB/s"] / peak, "traffic": None, "peak_source": peak_src},
+        "bf16_same_context": out["bf16"], "nvfp4": out["nvfp4"],
+        "nvfp4_speedup_over_bf16": out["bf16"]["ms_per_token"] / out["nvfp4"]["ms_per_token"],
+        "gpu_launches": 2 * args.steps * ntok, "cpu_baseline": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_tp(args, rank, world, local):
     """One sequence, model split over the ranks; world == 1 runs the whole model."""
     from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder, pick_num_attention_partitions
@@ -393,13 +531,17 @@ def run_tp(args, rank, world, local):
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     kv_heads_here = cfg["num_key_value_heads"] // world
     partitions = min(pick_num_attention_partitions(ctx, ntok), max(1, sms // kv_heads_here)) if ctx >= 512 else 1
+    fp4 = args.weights == "nvfp4"
     if world > 1:
-        dec = TensorParallelDecoder(model, rank, world, num_attention_partitions=partitions)
+        dec = TensorParallelDecoder(model, rank, world, num_attention_partitions=partitions, nvfp4_weights=fp4)
         mk = dec.mk
     else:
+        from thor_megakernels_b200 import nvfp4
+
         sched = LatencyScheduleBuilder.build(model, skip_attn_reduction=partitions == 1, num_attention_partitions=partitions)
         tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
-        mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data)
+        mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data,
+                                     quantized=nvfp4.quantize_model(model) if fp4 else None)
         sched.globs.barriers.zero_()
     stream = torch.cuda.current_stream(device)
     first = torch.tensor([17], dtype=torch.int32, device=device)
@@ -456,15 +598,17 @@ def run_tp(args, rank, world, local):
     if rank == 0:
         peak, peak_src = measured_hbm_peak()
         kv = kv_bytes_per_position(cfg)
-        total_bytes = sum(linear_weight_bytes(cfg) + kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
+        weight_bytes = linear_weight_bytes(cfg) * (0.5625 / 2.0 if fp4 else 1.0)
+        total_bytes = sum(weight_bytes + kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
         launch_ms = elapsed_ms / launches
         achieved = total_bytes / world / (launch_ms / 1000.0) / 1e9  # per GPU: every rank streams 1/world of the bytes
         line = {
             "metric": "decode_tokens_per_s", "value": launches / (elapsed_ms / 1000.0), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations and KV, NVFP4 weights" if fp4 else "bf16", "data": "synthetic",
             "config": {
-                "workload": f"{args.workload}: {'SELF-TEST 2-layer ' if args.self_test else ''}batch-1 greedy decode, "
+                "workload": f"{args.workload} ({args.weights} weights): {'SELF-TEST 2-layer ' if args.self_test else ''}batch-1 greedy decode, "
                             f"{ctx} cached positions, {ntok} tokens per step",
                 "step": f"{ntok} megakernel launches per rank",
                 "ms_per_token": launch_ms,
@@ -496,8 +640,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tokens", type=int, default=4, help="decode tokens timed for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="llama1b", choices=["llama1b", *TP_WORKLOADS],
+    ap.add_argument("--workload", default="llama1b", choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k"],
                     help="llama1b: the headline workload (replicas when N > 1); *-tp: one sequence split over the GPUs")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"], help="weight format of the *-tp workloads")
     ap.add_argument("--self-test", action="store_true",
                     help="2-layer, 4096-token-vocabulary model to exercise this script quickly; not a benchmark")
     args = ap.parse_args()
@@ -507,6 +652,10 @@ def main():
     try:
         if args.impl == "reference":
             run_reference(args, rank, world)
+        elif args.workload == "gemv":
+            run_gemv(args, rank, world, local)
+        elif args.workload == "llama1b-nvfp4-4k":
+            run_long_context(args, rank, world, local)
         elif args.workload != "llama1b":
             run_tp(args, rank, world, local)
         else:

@@ -106,6 +106,7 @@ struct Params {
     int o_cols, o_chunks, o_width;  // output projection: input columns (Hq*D), tiles per row block, columns per tile
     int down_width;   // columns of one down-projection slice (multiple of 256, at most 2048)
     int down_slices;  // inter / down_width
+    int down_owner_last;  // 1: the last slice's instruction folds a row block at once (see fold_down_blocks)
     int down_total;   // (hidden / 16) * down_slices
     // weights
     const bf16 *qkv_w, *attn_norm_w, *o_w, *mlp_norm_w, *up_w, *gate_w, *down_w, *lm_norm_w, *lm_w, *embed_w;
@@ -1219,16 +1220,16 @@ __device__ __forceinline__ void tp_push(const Params &p, uint32_t tag, int which
         st_tagged_sys(xchg_partials(p, r, tag, which, layer) + (size_t)p.tp_rank * p.hidden + row, __float_as_uint(v), tag);
 }
 
-// Receiving side for row blocks [b0, b1): two blocks at a time (lane = block
+// Receiving side for row blocks b0, b0 + stride, ... below b1: two blocks at a time (lane = block
 // parity x row), all ranks' cells in flight at once and retried as a set until
 // every tag matches; then residual + bf16(sum) goes to `out` as residual-stream
 // cells.  The residual comes from `plain` (layer-0 input) or from `resid` cells.
 __device__ void tp_fold_blocks(const Params &p, Smem &s, int lane, uint32_t tag, int which, int layer, int b0, int b1,
-                               const bf16 *plain, const unsigned long long *resid, unsigned long long *out, int op,
-                               int slot) {
+                               int stride, const bf16 *plain, const unsigned long long *resid, unsigned long long *out,
+                               int op, int slot) {
     const unsigned long long *mine = xchg_partials(p, p.tp_rank, tag, which, layer);
-    for (int c0 = b0; c0 < b1; c0 += 2) {
-        const int b = c0 + (lane >> 4);
+    for (int c0 = b0; c0 < b1; c0 += 2 * stride) {
+        const int b = c0 + (lane >> 4) * stride;
         const bool valid = b < b1;
         const int row = (valid ? b : c0) * kBlockRows + (lane & 15);
         unsigned long long v[kMaxRanks];
@@ -1261,6 +1262,111 @@ __device__ void tp_fold_blocks(const Params &p, Smem &s, int lane, uint32_t tag,
     }
 }
 
+// Folds the column slices of down-projection row blocks into the residual
+// stream (layer output).  Which blocks an instruction folds:
+//   * normally block b belongs to the instruction holding slice (b mod slices) of
+//     it, so the work is spread evenly over the SMs; the caller runs this only
+//     after the SM has parked all of its own slices of the layer, so the SMs never
+//     wait for one another in a cycle;
+//   * with p.down_owner_last (queues in which a layer's down-projection
+//     instructions are not consecutive) the instruction of the LAST slice folds
+//     its blocks right away: it then only waits for slices that precede it in the
+//     schedule's dependency order.
+// Up to `group` blocks are fetched together, all slices (the SM's own included,
+// read back from the cells) with every load in flight at once, and the set is
+// retried until every cell carries this launch's tag.  The fold runs in slice
+// order: with the interpreter's numerics each slice is rounded to bf16 and added
+// with a bf16 rounding (its sequential `hidden += partial`, python_vm.py:59-80);
+// with model numerics the slices are summed in fp32, scaled and rounded once.
+__device__ void fold_down_blocks(const Params &p, Smem &s, int lane, uint32_t tag, const int *ins, int slot,
+                                 long long t_start) {
+    const int op = 6;
+    const bool writer = lane < kBlockRows, pair_writer = writer && (lane & 1) == 0;
+    const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
+    const int S = p.down_slices;
+    unsigned long long *slice0 = p.t_down + ((size_t)layer * S) * p.hidden;
+    int first, step;
+    if (p.down_owner_last) {
+        first = red == S - 1 ? b0 : b1;
+        step = 1;
+    } else {
+        first = b0 + ((red - b0 % S) % S + S) % S;
+        step = S;
+    }
+    const int group = max(1, min(kDownGroup, (32 * kFetchPerLane) / (kBlockRows * S)));
+    for (int g0 = first; g0 < b1; g0 += group * step) {
+        const int nb = min(group, (b1 - g0 + step - 1) / step);
+        const int ncell = nb * S * kBlockRows;
+        unsigned long long pv[kFetchPerLane], rv[kDownGroup];
+        Deadline dl = start_deadline();
+        while (true) {
+            bool ok = true;
+#pragma unroll
+            for (int j = 0; j < kFetchPerLane; ++j) {
+                const int idx = lane + 32 * j;
+                if (idx < ncell) {
+                    const int i = idx / (S * kBlockRows), rem = idx - i * S * kBlockRows;
+                    pv[j] = ld_tagged1(slice0 + (size_t)(rem >> 4) * p.hidden + (g0 + i * step) * kBlockRows + (rem & 15));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kDownGroup; ++i)
+                if (i < nb && pair_writer)
+                    rv[i] = ld_tagged1(p.t_resid + ((size_t)layer * p.hidden + (g0 + i * step) * kBlockRows + lane) / 2);
+#pragma unroll
+            for (int j = 0; j < kFetchPerLane; ++j)
+                if (lane + 32 * j < ncell) ok &= tag_ok(pv[j], tag);
+#pragma unroll
+            for (int i = 0; i < kDownGroup; ++i)
+                if (i < nb && pair_writer) ok &= tag_ok(rv[i], tag);
+            if (__all_sync(0xffffffffu, ok) || !keep_waiting(p, s, dl, op, slot, 3)) break;
+        }
+        if (lane == 0) stamp(p, slot, 56, t_start);  // all slices present
+#pragma unroll
+        for (int j = 0; j < kFetchPerLane; ++j) {
+            const int idx = lane + 32 * j;
+            if (idx < ncell) {
+                const int i = idx / (S * kBlockRows), rem = idx - i * S * kBlockRows;
+                s.down_parts[i][rem >> 4][rem & 15] = __uint_as_float(tag_payload(pv[j]));
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < kDownGroup; ++i) {
+            if (i >= nb) break;
+            const int block = g0 + i * step;
+            if (p.tp_world > 1) {
+                // the local slices are a partial sum over this rank's columns: send it to every rank
+                if (writer && !aborted(s)) {
+                    float total = 0.f;
+                    for (int sl = 0; sl < S; ++sl) total += s.down_parts[i][sl][lane];
+                    tp_push(p, tag, 1, layer, block * kBlockRows + lane, total * down_scale(p, layer));
+                }
+                continue;
+            }
+            // residual pair (rows lane, lane+1) is held by the even lane
+            const uint32_t pr = __shfl_sync(0xffffffffu, tag_payload(rv[i]), lane & ~1);
+            float h = (lane & 1) ? bf16_hi(pr) : bf16_lo(pr);
+            if (writer) {
+                float total = 0.f;
+                for (int sl = 0; sl < S; ++sl) {
+                    const float part = s.down_parts[i][sl][lane];
+                    if (p.model_numerics) total += part;
+                    else h = round_bf16(h + round_bf16(part));
+                }
+                if (p.model_numerics) h = round_bf16(h + round_bf16(total * down_scale(p, layer)));
+            }
+            const float h_next = __shfl_xor_sync(0xffffffffu, h, 1);
+            if (pair_writer && !aborted(s))
+                st_tagged(p.t_hidden + ((size_t)layer * p.hidden + block * kBlockRows + lane) / 2, pack_bf16x2(h, h_next), tag);
+        }
+        __syncwarp();
+    }
+    if (p.tp_world > 1 && first < b1)
+        tp_fold_blocks(p, s, lane, tag, 1, layer, first, b1, step, nullptr, p.t_resid + (size_t)layer * (p.hidden / 2),
+                       p.t_hidden + (size_t)layer * (p.hidden / 2), op, slot);
+}
+
 template <int NCH>
 __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_start) {
     StorerState st;
@@ -1271,6 +1377,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
     if (p.flags & MK_STEP_EMBED) step_input = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
     const bool writer = lane < kBlockRows;              // lanes that own an output row
     const bool pair_writer = writer && (lane & 1) == 0;  // ... and write the cell of rows (lane, lane+1)
+    int run_start = -1, run_layer = -1;                 // consecutive down-projection instructions of one layer
 
 #pragma unroll 1
     for (int slot = 0; slot < p.queue_len; ++slot) {
@@ -1355,7 +1462,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                     const float y = collect_block(p, s, st, lane, op, slot) * ts;
                     if (writer && !aborted(s)) tp_push(p, tag, 0, layer, b * kBlockRows + lane, y);
                 }
-                tp_fold_blocks(p, s, lane, tag, 0, layer, b0, b1, layer == 0 ? step_input : nullptr,
+                tp_fold_blocks(p, s, lane, tag, 0, layer, b0, b1, 1, layer == 0 ? step_input : nullptr,
                                p.t_hidden + (size_t)(layer > 0 ? layer - 1 : 0) * (p.hidden / 2),
                                p.t_resid + (size_t)layer * (p.hidden / 2), op, slot);
                 publish(p, s, lane, counter(p, layer, 3, 0), b1 - b0);
@@ -1403,104 +1510,33 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             break;
         }
         case 6: {
-            // fp32 sum over one 2048-column slice of a row block, parked per slice.
-            // The instruction that owns the LAST slice of a row block also folds all
-            // of that block's slices into the residual stream, always in slice order:
-            // with the interpreter's numerics each slice is rounded to bf16 and added
-            // with a bf16 rounding (its sequential `hidden += partial`,
-            // python_vm.py:59-80); with model numerics the slices are summed in fp32,
-            // scaled and rounded once.  The other slices are waited for cell by cell,
-            // so no ordering between the slice producers is needed.
+            // fp32 sum over one column slice of a row block, parked per slice as a
+            // tagged cell; folding the slices into the residual stream is a separate
+            // step (fold_down_blocks), run once this SM has parked all of its slices
+            // of the layer.
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
-            const bool owner = red == p.down_slices - 1;
-            unsigned long long *slice0 = p.t_down + ((size_t)layer * p.down_slices) * p.hidden;
-            // The owner fetches the other slices of up to `group` row blocks with all
-            // loads in flight at once (kFetchPerLane cells per lane) and retries the
-            // whole set until every cell carries this launch's tag: one L2 round trip
-            // after the last producer's store, however many blocks the instruction has.
-            const int group = owner && red > 0 ? max(1, min(kDownGroup, (32 * kFetchPerLane) / (kBlockRows * red))) : kDownGroup;
-            for (int c0 = b0; c0 < b1; c0 += group) {
-                const int nb = min(group, b1 - c0);
-                for (int i = 0; i < nb; ++i) {
-                    const float y = collect_block(p, s, st, lane, op, slot);
-                    const int row = (c0 + i) * kBlockRows + (lane & 15);
-                    if (writer && !aborted(s)) st_tagged(slice0 + (size_t)red * p.hidden + row, __float_as_uint(y), tag);
-                    if (writer) s.down_parts[i][red][lane] = y;
-                }
-                if (!owner) continue;
-                if (lane == 0) stamp(p, slot, 55, t_start);  // own slices parked
-                const int ncell = nb * red * kBlockRows;
-                unsigned long long pv[kFetchPerLane], rv[kDownGroup];
-                Deadline dl = start_deadline();
-                while (true) {
-                    bool ok = true;
-#pragma unroll
-                    for (int j = 0; j < kFetchPerLane; ++j) {
-                        const int idx = lane + 32 * j;
-                        if (idx < ncell) {
-                            const int i = idx / (red * kBlockRows), rem = idx - i * red * kBlockRows;
-                            pv[j] = ld_tagged1(slice0 + (size_t)(rem >> 4) * p.hidden + (c0 + i) * kBlockRows + (rem & 15));
-                        }
-                    }
-#pragma unroll
-                    for (int i = 0; i < kDownGroup; ++i)
-                        if (i < nb && pair_writer)
-                            rv[i] = ld_tagged1(p.t_resid + ((size_t)layer * p.hidden + (c0 + i) * kBlockRows + lane) / 2);
-#pragma unroll
-                    for (int j = 0; j < kFetchPerLane; ++j)
-                        if (lane + 32 * j < ncell) ok &= tag_ok(pv[j], tag);
-#pragma unroll
-                    for (int i = 0; i < kDownGroup; ++i)
-                        if (i < nb && pair_writer) ok &= tag_ok(rv[i], tag);
-                    if (__all_sync(0xffffffffu, ok) || !keep_waiting(p, s, dl, op, slot, 3)) break;
-                }
-                if (lane == 0) {
-                    stamp(p, slot, 56, t_start);  // other slices present
-                    if (p.flags & MK_STEP_TIMINGS) p.timings[((size_t)blockIdx.x * p.queue_len + slot) * kTimingSlots + 57] = (int)dl.it;
-                }
-#pragma unroll
-                for (int j = 0; j < kFetchPerLane; ++j) {
-                    const int idx = lane + 32 * j;
-                    if (idx < ncell) {
-                        const int i = idx / (red * kBlockRows), rem = idx - i * red * kBlockRows;
-                        s.down_parts[i][rem >> 4][rem & 15] = __uint_as_float(tag_payload(pv[j]));
-                    }
-                }
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < kDownGroup; ++i) {
-                    if (i >= nb) break;
-                    if (p.tp_world > 1) {
-                        // the local slices are a partial sum over this rank's columns: send it to every rank
-                        if (writer && !aborted(s)) {
-                            float total = 0.f;
-                            for (int sl = 0; sl <= red; ++sl) total += s.down_parts[i][sl][lane];
-                            tp_push(p, tag, 1, layer, (c0 + i) * kBlockRows + lane, total * down_scale(p, layer));
-                        }
-                        continue;
-                    }
-                    // residual pair (rows lane, lane+1) is held by the even lane
-                    const uint32_t pr = __shfl_sync(0xffffffffu, tag_payload(rv[i]), lane & ~1);
-                    float h = (lane & 1) ? bf16_hi(pr) : bf16_lo(pr);
-                    if (writer) {
-                        float total = 0.f;
-                        for (int sl = 0; sl <= red; ++sl) {
-                            const float part = s.down_parts[i][sl][lane];
-                            if (p.model_numerics) total += part;
-                            else h = round_bf16(h + round_bf16(part));
-                        }
-                        if (p.model_numerics) h = round_bf16(h + round_bf16(total * down_scale(p, layer)));
-                    }
-                    const float h_next = __shfl_xor_sync(0xffffffffu, h, 1);
-                    if (pair_writer && !aborted(s))
-                        st_tagged(p.t_hidden + ((size_t)layer * p.hidden + (c0 + i) * kBlockRows + lane) / 2,
-                                  pack_bf16x2(h, h_next), tag);
-                }
-                __syncwarp();
+            unsigned long long *mine = p.t_down + ((size_t)layer * p.down_slices + red) * p.hidden;
+            for (int b = b0; b < b1; ++b) {
+                const float y = collect_block(p, s, st, lane, op, slot);
+                if (writer && !aborted(s)) st_tagged(mine + b * kBlockRows + lane, __float_as_uint(y), tag);
             }
-            if (owner && p.tp_world > 1)
-                tp_fold_blocks(p, s, lane, tag, 1, layer, b0, b1, nullptr, p.t_resid + (size_t)layer * (p.hidden / 2),
-                               p.t_hidden + (size_t)layer * (p.hidden / 2), op, slot);
+            if (lane == 0) stamp(p, slot, 55, t_start);  // own slices parked
+            if (p.down_owner_last) {
+                fold_down_blocks(p, s, lane, tag, ins, slot, t_start);
+            } else {
+                if (run_start < 0 || run_layer != layer) { run_start = slot; run_layer = layer; }
+                int nxt = slot + 1;
+                while (nxt < p.queue_len && __ldg(instruction_at(p, nxt)) == 0) ++nxt;
+                const bool more = nxt < p.queue_len && __ldg(instruction_at(p, nxt)) == 6 &&
+                                  __ldg(instruction_at(p, nxt) + 1) == layer;
+                if (!more) {
+                    for (int sl = run_start; sl <= slot; ++sl) {
+                        const int *other = instruction_at(p, sl);
+                        if (__ldg(other) == 6 && __ldg(other + 1) == layer) fold_down_blocks(p, s, lane, tag, other, slot, t_start);
+                    }
+                    run_start = -1;
+                }
+            }
             publish(p, s, lane, counter(p, layer, 5, 0), b1 - b0);
             break;
         }
@@ -1878,6 +1914,34 @@ extern "C" int mk_set_schedule(void *handle, const int32_t *instructions, int32_
         return fail(MK_ERR_RESIDENCY, "worker grid (%d) exceeds co-resident capacity (%d SMs x %d)", workers, h->sm_count, h->resident);
     if (workers > h->sm_count)
         return fail(MK_ERR_RESIDENCY, "worker grid (%d) exceeds the physical SM count (%d)", workers, h->sm_count);
+    // Down-projection folding mode (fold_down_blocks): spreading the folds over all
+    // SMs needs every queue to hold a layer's down-projection instructions (opcode 6)
+    // consecutively, which the reference's assignment policies all produce.  Any
+    // other ordering gets the mode in which only the last slice's instruction folds.
+    int owner_last = 0;
+    if (queue_len > 0) {
+        const size_t words = (size_t)workers * queue_len * kInstrWords;
+        int32_t *host = new (std::nothrow) int32_t[words];
+        if (!host) return fail(MK_ERR_BAD_ARGUMENT, "mk_set_schedule: out of host memory");
+        cudaError_t e = cudaMemcpy(host, instructions, words * sizeof(int32_t), cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) { delete[] host; return cuda_fail(e, "cudaMemcpy(instructions)"); }
+        for (int w = 0; w < workers && !owner_last; ++w) {
+            int run_layer = -1;            // layer of the run of opcode-6 instructions being read, -1 outside a run
+            unsigned long long seen = 0;   // layers whose run has ended (layers >= 64 fall back at once)
+            for (int q = 0; q < queue_len; ++q) {
+                const int32_t *ins = host + ((size_t)w * queue_len + q) * kInstrWords;
+                if (ins[0] == 0) continue;
+                const int layer = ins[0] == 6 ? ins[1] : -1;
+                if (layer != run_layer) {
+                    if (run_layer >= 0) seen |= 1ull << run_layer;
+                    run_layer = layer;
+                    if (layer >= 64 || (layer >= 0 && (seen >> layer) & 1ull)) { owner_last = 1; break; }
+                }
+            }
+        }
+        delete[] host;
+    }
+    h->params.down_owner_last = owner_last;
     h->params.instructions = instructions;
     h->params.timings = timings;
     h->params.workers = workers;

@@ -29,11 +29,17 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--pos", type=int, default=60)
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--nvfp4", action="store_true", help="NVFP4 weight-only linears instead of bf16 weights")
     args = ap.parse_args()
     if args.layers is not None:
         bench.MODEL.update(num_hidden_layers=args.layers)
     model, sched = bench.build_gpu_model(torch.device("cuda:0"))
-    mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data)
+    quantized = None
+    if args.nvfp4:
+        from thor_megakernels_b200.nvfp4 import quantize_model
+
+        quantized = quantize_model(model)
+    mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
     tok = torch.tensor([17], dtype=torch.int32, device="cuda")
     out = torch.zeros(1, dtype=torch.int32, device="cuda")
     flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN

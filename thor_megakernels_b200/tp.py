@@ -112,7 +112,7 @@ class TensorParallelDecoder:
     the same arguments and returns the same tokens on every rank."""
 
     def __init__(self, model, rank: int, world: int, schedule: str = "rr", group=None,
-                 num_attention_partitions: int = 1):
+                 num_attention_partitions: int = 1, nvfp4_weights: bool = False):
         import torch.distributed as dist
 
         from .demos.latency.scheduler import LatencyScheduleBuilder
@@ -125,8 +125,14 @@ class TensorParallelDecoder:
         self.schedule = LatencyScheduleBuilder.build(self.local, skip_attn_reduction=not split,
                                                      num_attention_partitions=num_attention_partitions)
         tensorize_instructions(self.schedule.globs, assign_to_sms(schedule, schedule=self.schedule))
+        quantized = None
+        if nvfp4_weights:  # every rank quantises its own shard (block scales run along K, which only o/down split)
+            from .nvfp4 import quantize_model
+
+            quantized = quantize_model(self.local)
         self.mk = Megakernel.from_globals(self.schedule.globs,
-                                          embed_w=model.model.embed_tokens.embed_tokens.weight.data)
+                                          embed_w=model.model.embed_tokens.embed_tokens.weight.data,
+                                          quantized=quantized)
         self.schedule.globs.barriers.zero_()
         mine = self.mk.tp_init(rank, world, self.local.vocab_offset)
         handles: list = [None] * world
