@@ -202,6 +202,9 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
 /* Tuning knobs without a counterpart in the reference (its equivalents are
  * compile-time constants, include/config.cuh:7-72). */
 #define MK_OPT_WAIT_BUDGET_CYCLES 0  /* same as mk_set_wait_budget */
+#define MK_OPT_DOWN_FOLD_LAST     3  /* 1: only the instruction of a row block's last column slice folds the slices into the
+                                      * residual stream (chosen automatically for queues whose down-projection
+                                      * instructions of a layer are not consecutive); 0: folds spread over all SMs */
 #define MK_OPT_MAX_INFLIGHT_TILES 2  /* weight tiles (64 KiB bf16 / 18 KiB NVFP4) one loader keeps in flight */
 #define MK_OPT_EARLY_POLL_SHIFT   1  /* consumers stop watching a dependency counter and poll the data cells
                                       * themselves once it is within target >> shift of its target; 31 = never */

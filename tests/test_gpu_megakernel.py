@@ -241,6 +241,36 @@ def test_launch_facts_and_admission_errors(tiny):
     assert torch.equal(before, g.hidden_states)
 
 
+def test_both_down_projection_fold_modes_give_identical_results(tiny):
+    """Row blocks folded by the SM that holds slice (block mod slices), or all by
+    the last slice's SM (the mode for queues that do not keep a layer's
+    down-projection instructions together): same slice order, same bits."""
+    from thor_megakernels_b200._lib import MK_OPT_DOWN_FOLD_LAST
+    from thor_megakernels_b200.generators import MK_FusedGenerator
+
+    meta, arrays, model = tiny
+    sched = build_schedule(model)
+    first, ntok = int(arrays["tokens"][0]), 5
+    seen = []
+    for forced in (0, 1):
+        n = load_prefill(model, arrays)
+        model.stacked_kv_cache[0][:, :, n:] = 0
+        model.stacked_kv_cache[1][:, :, n:] = 0
+        gen = MK_FusedGenerator(model, sched)
+        gen.mk.set_option(MK_OPT_DOWN_FOLD_LAST, forced)
+        out = torch.zeros((1, ntok + 1), dtype=torch.long, device="cuda")
+        out[0, 0] = first
+        gen.generate(out, prompt_len=n, ntok=ntok)
+        torch.cuda.synchronize()
+        assert gen.mk.status()["code"] == 0
+        seen.append((out.tolist(), sched.globs.hidden_states.clone(), sched.globs.logits.clone(),
+                     model.stacked_kv_cache[0][:, 0, n:n + ntok].clone()))
+        gen.mk.close()
+    assert seen[0][0] == seen[1][0]
+    for a, b in zip(seen[0][1:], seen[1][1:]):
+        assert torch.equal(a, b)
+
+
 def test_bounded_wait_reports_status_instead_of_hanging(tiny):
     """A dependency counter that nothing ever raises: the wait runs out, the
     kernel returns, the status words say which worker/opcode/slot gave up, and

@@ -25,6 +25,7 @@ MK_TP_HANDLE_BYTES = 64
 MK_OPT_WAIT_BUDGET_CYCLES = 0
 MK_OPT_EARLY_POLL_SHIFT = 1
 MK_OPT_MAX_INFLIGHT_TILES = 2
+MK_OPT_DOWN_FOLD_LAST = 3
 
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1

@@ -1704,6 +1704,8 @@ struct Handle {
     // tensor parallelism
     void *xchg = nullptr;              // this GPU's exchange buffer (cudaMalloc, exported over CUDA IPC)
     size_t xchg_bytes = 0;
+    int fold_last_detected = 0;        // some queue holds a layer's down-projection instructions apart
+    int fold_last_forced = 0;          // MK_OPT_DOWN_FOLD_LAST
     int tp_world_pending = 0;          // set by mk_tp_init, becomes params.tp_world in mk_tp_connect
     void *peer_xchg[kMaxRanks] = {};   // peers' buffers opened over CUDA IPC
 };
@@ -1941,7 +1943,8 @@ extern "C" int mk_set_schedule(void *handle, const int32_t *instructions, int32_
         }
         delete[] host;
     }
-    h->params.down_owner_last = owner_last;
+    h->fold_last_detected = owner_last;
+    h->params.down_owner_last = owner_last || h->fold_last_forced;
     h->params.instructions = instructions;
     h->params.timings = timings;
     h->params.workers = workers;
@@ -2036,6 +2039,10 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     case MK_OPT_MAX_INFLIGHT_TILES:
         if (value < 1) return fail(MK_ERR_BAD_ARGUMENT, "at least one tile must be in flight");
         h->params.max_inflight = (int)(value > kMaxStages ? kMaxStages : value);
+        return 0;
+    case MK_OPT_DOWN_FOLD_LAST:
+        h->fold_last_forced = value != 0;
+        h->params.down_owner_last = h->fold_last_detected || h->fold_last_forced;
         return 0;
     case MK_OPT_EARLY_POLL_SHIFT:
         if (value < 0 || value > 31) return fail(MK_ERR_BAD_ARGUMENT, "early-poll shift must be 0..31");
