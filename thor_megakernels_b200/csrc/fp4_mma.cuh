@@ -32,6 +32,28 @@ __device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
     return (uint32_t)h.x | ((uint32_t)h.y << 16);
 }
 
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// Four E2M1 codes -> two f16x2 (codes 0,1 and codes 2,3), by table look-up: the
+// magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 are f16 values whose low byte is zero, so
+// one byte permute with the 3-bit magnitudes as selectors fetches the four high
+// bytes at once; a second permute in sign-replication mode turns the codes' sign
+// bits into byte masks.  `w` holds eight codes, `w4 = w << 4`, `half` picks codes
+// 0..3 or 4..7 of the word.
+__device__ __forceinline__ void e2m1x4_to_f16x4(uint32_t w, uint32_t w4, int half, uint32_t &p01, uint32_t &p23) {
+    const uint32_t sel = (half ? (w >> 16) : w) & 0x7777u;
+    const uint32_t mag = prmt(0x3E3C3800u, 0x46444240u, sel);
+    // even codes have their sign in bit 7 of a byte of w4, odd codes in bit 7 of a byte of w
+    const uint32_t sign = prmt(w, w4, half ? 0xBFAEu : 0x9D8Cu);
+    const uint32_t hb = mag | (sign & 0x80808080u);
+    p01 = prmt(hb, 0u, 0x1404u);
+    p23 = prmt(hb, 0u, 0x3424u);
+}
+
 // One E4M3 scale byte -> the same f16 value in both halves.
 __device__ __forceinline__ uint32_t e4m3_to_f16x2_dup(uint32_t byte) {
     const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(byte & 0xffu), __NV_E4M3);
@@ -61,6 +83,7 @@ __device__ __forceinline__ void fp4_rows_mma(float (&acc)[4], const uint4 (&code
                             codes_g[1].x, codes_g[1].y, codes_g[1].z, codes_g[1].w};
     const uint32_t wh[8] = {codes_h[0].x, codes_h[0].y, codes_h[0].z, codes_h[0].w,
                             codes_h[1].x, codes_h[1].y, codes_h[1].z, codes_h[1].w};
+    float acc2[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the chain of dependent MMAs
 #pragma unroll
     for (int blk = 0; blk < 4; ++blk) {  // one 16-column scale block = 8 code bytes = 2 words
         const uint32_t sg = e4m3_to_f16x2_dup(sc_g >> (8 * blk));
@@ -68,17 +91,22 @@ __device__ __forceinline__ void fp4_rows_mma(float (&acc)[4], const uint4 (&code
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const uint32_t cg = wg[2 * blk + half], ch = wh[2 * blk + half];
+            const uint32_t cg4 = cg << 4, ch4 = ch << 4;
 #pragma unroll
             for (int pair = 0; pair < 2; ++pair) {  // an MMA takes 2 bytes (4 codes) per row
                 const int i = (2 * blk + half) * 2 + pair;  // MMA index 0..15, columns 4i..4i+3 of the lane
-                const uint32_t a0 = hmul2_bits(e2m1x2_to_f16x2(cg >> (16 * pair)), sg);
-                const uint32_t a2 = hmul2_bits(e2m1x2_to_f16x2(cg >> (16 * pair + 8)), sg);
-                const uint32_t a1 = hmul2_bits(e2m1x2_to_f16x2(ch >> (16 * pair)), sh);
-                const uint32_t a3 = hmul2_bits(e2m1x2_to_f16x2(ch >> (16 * pair + 8)), sh);
-                mma_f16_16816(acc, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
+                uint32_t g01, g23, h01, h23;
+                e2m1x4_to_f16x4(cg, cg4, pair, g01, g23);
+                e2m1x4_to_f16x4(ch, ch4, pair, h01, h23);
+                const uint32_t a0 = hmul2_bits(g01, sg), a2 = hmul2_bits(g23, sg);
+                const uint32_t a1 = hmul2_bits(h01, sh), a3 = hmul2_bits(h23, sh);
+                if (i & 1) mma_f16_16816(acc2, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
+                else mma_f16_16816(acc, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
             }
         }
     }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) acc[r] += acc2[r];
 }
 
 // Same, with the activation operand kept as eight 16-byte vectors.

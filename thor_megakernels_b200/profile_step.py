@@ -29,11 +29,32 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--pos", type=int, default=60)
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--arch", default="1b", choices=["1b", "8b"], help="8b: Llama-3.1-8B layer shapes, --pos cached positions")
+    ap.add_argument("--partitions", type=int, default=18, help="attention slices per KV head (8b only)")
     ap.add_argument("--nvfp4", action="store_true", help="NVFP4 weight-only linears instead of bf16 weights")
     args = ap.parse_args()
-    if args.layers is not None:
-        bench.MODEL.update(num_hidden_layers=args.layers)
-    model, sched = bench.build_gpu_model(torch.device("cuda:0"))
+    if args.arch == "8b":
+        # Llama-3.1-8B layer shapes with a long cache (attention split into slices), few layers to keep the capture small
+        from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
+        from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+        from thor_megakernels_b200.model_types import ExtraModelConfig
+        from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+        cfg = dict(bench.MODEL_8B, num_hidden_layers=args.layers or 4)
+        device = torch.device("cuda:0")
+        extra = ExtraModelConfig(interleave_rope=True, max_len_override=args.pos + 16)
+        model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=4, device=device, generate_on=device)
+        gen = torch.Generator(device=device).manual_seed(3)
+        for cache in model.stacked_kv_cache:
+            cache[:, :, :args.pos] = torch.randn(cache[:, :, :args.pos].shape, generator=gen, device=device).bfloat16()
+        sched = LatencyScheduleBuilder.build(model, skip_attn_reduction=args.partitions == 1,
+                                             num_attention_partitions=args.partitions)
+        tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+        sched.globs.barriers.zero_()
+    else:
+        if args.layers is not None:
+            bench.MODEL.update(num_hidden_layers=args.layers)
+        model, sched = bench.build_gpu_model(torch.device("cuda:0"))
     quantized = None
     if args.nvfp4:
         from thor_megakernels_b200.nvfp4 import quantize_model
