@@ -41,10 +41,15 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     if not force and not is_stale():
         return LIBRARY
     sources = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    cmd = [find_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(LIBRARY), *sources]
+    # Build beside the target and rename: several ranks may find the library stale at the same moment,
+    # and none of them must ever load a half-written file.
+    scratch = LIBRARY.with_name(f"{LIBRARY.name}.{os.getpid()}.tmp")
+    cmd = [find_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(scratch), *sources]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
+        scratch.unlink(missing_ok=True)
         raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+    os.replace(scratch, LIBRARY)
     if verbose:
         print(proc.stderr)
     return LIBRARY
