@@ -18,16 +18,22 @@ synthetic weights N(0, 0.02), synthetic prompt/KV).  The JSON line reports
                  interpreter) timed on this box's cores over a few tokens.
 
 ``--impl reference`` times only that CPU interpreter (one token per step).
-With N > 1 (under torchrun) every rank decodes an independent replica of that
-workload (weak scaling: a 1B model at batch 1 gains nothing from being split).
 
-``--workload llama8b-tp`` (or ``llama1b-tp``) instead splits ONE sequence's
-model over the N GPUs (tensor parallel, all-reduces inside the kernel over
-NVLink peer memory; strong scaling; N = 1 runs the whole model on one GPU):
-Llama-3.1-8B architecture, bf16, batch 1, 8192 cached positions, 64 tokens per
-step.  ``--workload gemv`` times the single-operator GEMV (bf16 and NVFP4
-weights, batch 1 and 4); ``--workload llama1b-nvfp4-4k`` the NVFP4 weight-only
-megakernel against bf16 weights at 4096 cached positions.
+With N > 1 (under torchrun) the SAME request is decoded with the model split
+over the N GPUs (tensor parallel: heads, FFN columns and vocabulary sharded,
+the two all-reduces per layer inside the kernel over NVLink peer memory;
+``"scaling": "strong"``).  Before timing, a 2-layer model is decoded both split
+and whole and the agreement goes into ``tp_parity``.  At every N the line also
+carries ``llama8b_tp``: the Llama-3.1-8B architecture at batch 1 with 8192
+cached positions on the same N GPUs, bf16 and NVFP4 weight-only.
+
+Other workloads: ``--workload llama8b-tp`` / ``llama1b-tp`` run only the split
+decode; ``gemv`` the single-operator GEMV (bf16 and NVFP4 weights, batch 1 and
+4); ``llama1b-nvfp4-4k`` the NVFP4 weight-only megakernel against bf16 weights
+at 4096 cached positions; ``timeline`` one step with per-instruction clock
+stamps, summarised per opcode; ``profile-step`` a few bare steps for a profiler
+(``--arch 8b --layers 4 --pos 8192`` for the 8B shapes).  ``--schedule`` picks
+the queue assignment policy (rr, zz, wave, dag).
 """
 from __future__ import annotations
 
@@ -48,7 +54,7 @@ import torch  # noqa: E402
 
 PROMPT_LEN = 16
 TOKENS_PER_REQUEST = 100
-FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+FALLBACK_HBM_GBS = 6650.0  # used only when MEASURED_PEAKS.json is absent
 
 MODEL = dict(hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
              intermediate_size=8192, vocab_size=128256)
@@ -175,7 +181,21 @@ def max_over_ranks(x: float, world: int) -> float:
     return float(t.item())
 
 
-def build_gpu_model(device):
+def make_schedule(model, schedule: str, **kwargs):
+    """``b200``: the library's own layout (one SM owns all column slices of its
+    down-projection rows); rr / zz / wave / dag: the reference's layout under
+    that assignment policy."""
+    from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder, build_b200_schedule
+    from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+    if schedule == "b200":
+        return build_b200_schedule(model, **kwargs)
+    sched = LatencyScheduleBuilder.build(model, **kwargs)
+    tensorize_instructions(sched.globs, assign_to_sms(schedule, schedule=sched))
+    return sched
+
+
+def build_gpu_model(device, schedule: str = "b200"):
     from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
     from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
     from thor_megakernels_b200.model_types import ExtraModelConfig
@@ -186,9 +206,7 @@ def build_gpu_model(device):
     gen = torch.Generator(device=device).manual_seed(3)
     for cache in model.stacked_kv_cache:
         cache[:, :, :PROMPT_LEN] = torch.randn(cache[:, :, :PROMPT_LEN].shape, generator=gen, device=device).bfloat16()
-    sched = LatencyScheduleBuilder.build(model)
-    tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
-    return model, sched
+    return model, make_schedule(model, schedule)
 
 
 def time_cpu_oracle(model_gpu, tokens: int, threads: int, warm: int = 1):
@@ -269,7 +287,7 @@ def run_ours(args, rank, world, local):
         raise RuntimeError("bench.py measures the CUDA megakernel; no CUDA device is visible")
     device = torch.device(f"cuda:{local}")
     torch.cuda.set_device(device)
-    model, sched = build_gpu_model(device)
+    model, sched = build_gpu_model(device, schedule=args.schedule)
     gen = MK_FusedGenerator(model, sched)
     mk = gen.mk
     stream = torch.cuda.current_stream(device)
@@ -335,15 +353,15 @@ def run_ours(args, rank, world, local):
         line = {
             "metric": "decode_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {
                 "workload": ("SELF-TEST (2 layers, small vocabulary) - not the benchmark workload" if args.self_test else
                              "llama-3.2-1b-arch bf16 batch-1 greedy decode: 16-token context, 100 tokens (pos 16..115)"),
                 "step": "one 100-token request = 100 megakernel launches",
                 "ms_per_token": launch_ms,
                 "l2": "inputs larger than L2 (2.47 GB of weights streamed per launch vs 126 MB)",
-                "parallelism": "replicas" if world > 1 else "single",
-                "schedule": "reference latency schedule, round-robin, 148 queues",
+                "parallelism": "single",
+                "schedule": f"reference latency instruction set, layout/policy {args.schedule}, one queue per SM",
             },
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": MEASURED_DRAM_TRAFFIC_PER_LAUNCH, "peak_source": peak_src,
@@ -364,6 +382,12 @@ def run_ours(args, rank, world, local):
                                           f"interpreter (oracle/pyvm.py), {threads} threads"}
     elif rank == 0:
         line["cpu_baseline"] = None
+    if not args.no_8b and not args.self_test:
+        # the 1-GPU point of the Llama-3.1-8B curve; the 1B model is dropped first
+        gen.mk.close()
+        del gen, mk, model, sched
+        torch.cuda.empty_cache()
+        line["llama8b_tp"] = llama8b_records(args, rank, world, local)
     if rank == 0:
         print(json.dumps(line), flush=True)
 
@@ -458,8 +482,7 @@ def run_long_context(args, rank, world, local):
         cache[:, :, :ctx] = torch.randn(cache[:, :, :ctx].shape, generator=gen, device=device).bfloat16()
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     partitions = min(pick_num_attention_partitions(ctx, ntok), max(1, sms // cfg["num_key_value_heads"]))
-    sched = LatencyScheduleBuilder.build(model, skip_attn_reduction=False, num_attention_partitions=partitions)
-    tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+    sched = make_schedule(model, args.schedule, skip_attn_reduction=False, num_attention_partitions=partitions)
     peak, peak_src = measured_hbm_peak()
     kv = kv_bytes_per_position(cfg)
     kv_bytes = sum(kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
@@ -504,8 +527,10 @@ def run_long_context(args, rank, world, local):
     print(json.dumps(line), flush=True)
 
 
-def run_tp(args, rank, world, local):
-    """One sequence, model split over the ranks; world == 1 runs the whole model."""
+def measure_split_decode(workload: str, weights: str, steps: int, warmup: int, rank: int, world: int, local: int,
+                         schedule: str = "b200", self_test: bool = False, e2e: bool = True) -> dict | None:
+    """One sequence decoded with the model split over the ranks (world == 1: the
+    whole model on one GPU).  Every rank calls this; rank 0 gets the record."""
     from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder, pick_num_attention_partitions
     from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
     from thor_megakernels_b200.model_types import ExtraModelConfig
@@ -513,10 +538,8 @@ def run_tp(args, rank, world, local):
     from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
     from thor_megakernels_b200.tp import TensorParallelDecoder
 
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py measures the CUDA megakernel; no CUDA device is visible")
-    cfg, ctx, ntok, seed = TP_WORKLOADS[args.workload]
-    if args.self_test:
+    cfg, ctx, ntok, seed = TP_WORKLOADS[workload]
+    if self_test:
         cfg = dict(cfg, num_hidden_layers=2, vocab_size=4096)
     device = torch.device(f"cuda:{local}")
     torch.cuda.set_device(device)
@@ -531,17 +554,18 @@ def run_tp(args, rank, world, local):
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     kv_heads_here = cfg["num_key_value_heads"] // world
     partitions = min(pick_num_attention_partitions(ctx, ntok), max(1, sms // kv_heads_here)) if ctx >= 512 else 1
-    fp4 = args.weights == "nvfp4"
+    fp4 = weights == "nvfp4"
+    embed = model.model.embed_tokens.embed_tokens.weight.data
     if world > 1:
-        dec = TensorParallelDecoder(model, rank, world, num_attention_partitions=partitions, nvfp4_weights=fp4)
+        dec = TensorParallelDecoder(model, rank, world, schedule=schedule, num_attention_partitions=partitions,
+                                    nvfp4_weights=fp4)
         mk = dec.mk
+        del model  # every rank keeps only its shard (and the embedding table)
     else:
         from thor_megakernels_b200 import nvfp4
 
-        sched = LatencyScheduleBuilder.build(model, skip_attn_reduction=partitions == 1, num_attention_partitions=partitions)
-        tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
-        mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data,
-                                     quantized=nvfp4.quantize_model(model) if fp4 else None)
+        sched = make_schedule(model, schedule, skip_attn_reduction=partitions == 1, num_attention_partitions=partitions)
+        mk = Megakernel.from_globals(sched.globs, embed_w=embed, quantized=nvfp4.quantize_model(model) if fp4 else None)
         sched.globs.barriers.zero_()
     stream = torch.cuda.current_stream(device)
     first = torch.tensor([17], dtype=torch.int32, device=device)
@@ -550,7 +574,7 @@ def run_tp(args, rank, world, local):
     def request():
         mk.decode(first, produced, start_pos=ctx, count=ntok, stream=stream)
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         request()
     torch.cuda.synchronize(device)
     mk.status()
@@ -560,7 +584,7 @@ def run_tp(args, rank, world, local):
     sampler.start()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         request()
     end.record(stream)
     torch.cuda.synchronize(device)
@@ -568,63 +592,316 @@ def run_tp(args, rank, world, local):
     clocks = sampler.stop()
     mk.status()
     elapsed_ms = max_over_ranks(start.elapsed_time(end), world)
-    launches = args.steps * ntok
+    launches = steps * ntok
+    e2e_ms = None
+    if e2e:
+        host_first = torch.tensor([17], dtype=torch.int32).pin_memory()
+        host_out = torch.zeros(ntok, dtype=torch.int32).pin_memory()
 
-    host_first = torch.tensor([17], dtype=torch.int32).pin_memory()
-    host_out = torch.zeros(ntok, dtype=torch.int32).pin_memory()
+        def request_e2e():
+            first.copy_(host_first, non_blocking=True)
+            mk.decode(first, produced, start_pos=ctx, count=ntok, stream=stream)
+            host_out.copy_(produced, non_blocking=True)
+            stream.synchronize()
 
-    def request_e2e():
-        first.copy_(host_first, non_blocking=True)
-        mk.decode(first, produced, start_pos=ctx, count=ntok, stream=stream)
-        host_out.copy_(produced, non_blocking=True)
-        stream.synchronize()
-
-    for _ in range(2):
-        request_e2e()
-    barrier(world)
-    torch.cuda.synchronize(device)
-    start.record(stream)
-    for _ in range(args.steps):
-        request_e2e()
-    end.record(stream)
-    torch.cuda.synchronize(device)
-    e2e_ms = max_over_ranks(start.elapsed_time(end), world)
-    tokens = torch.zeros(world * ntok, dtype=torch.int32, device=device)
+        for _ in range(2):
+            request_e2e()
+        barrier(world)
+        torch.cuda.synchronize(device)
+        start.record(stream)
+        for _ in range(steps):
+            request_e2e()
+        end.record(stream)
+        torch.cuda.synchronize(device)
+        e2e_ms = max_over_ranks(start.elapsed_time(end), world)
     if world > 1:
         import torch.distributed as dist
 
+        tokens = torch.zeros(world * ntok, dtype=torch.int32, device=device)
         dist.all_gather_into_tensor(tokens, produced)
         assert all(torch.equal(tokens[r * ntok:(r + 1) * ntok], produced) for r in range(world)), "ranks produced different tokens"
+    mk.close()
+    if rank != 0:
+        return None
+    peak, peak_src = measured_hbm_peak()
+    kv = kv_bytes_per_position(cfg)
+    weight_bytes = linear_weight_bytes(cfg) * (0.5625 / 2.0 if fp4 else 1.0)
+    total_bytes = sum(weight_bytes + kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
+    launch_ms = elapsed_ms / launches
+    achieved = total_bytes / world / (launch_ms / 1000.0) / 1e9  # per GPU: every rank streams 1/world of the bytes
+    line = {
+        "metric": "decode_tokens_per_s", "value": launches / (elapsed_ms / 1000.0), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": elapsed_ms / steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 activations and KV, NVFP4 weights" if fp4 else "bf16", "data": "synthetic",
+        "config": {
+            "workload": f"{workload} ({weights} weights): {'SELF-TEST 2-layer ' if self_test else ''}batch-1 greedy decode, "
+                        f"{ctx} cached positions, {ntok} tokens per step",
+            "step": f"{ntok} megakernel launches per rank",
+            "ms_per_token": launch_ms,
+            "parallelism": f"tp{world}" if world > 1 else "single",
+            "attention_partitions_per_kv_head": partitions,
+            "schedule": schedule,
+            "l2": "inputs larger than L2",
+        },
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": total_bytes / world,
+                     "launch_ms": launch_ms, "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "note": "per GPU: total algorithmic bytes / n_gpus over the launch time"},
+        "gpu_launches": launches, "clocks": clocks, "cpu_baseline": None,
+    }
+    if e2e_ms is not None:
+        line["e2e"] = {"value": launches / (e2e_ms / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": 4,
+                       "d2h_bytes_per_step": 4 * ntok, "api": "Megakernel.decode on every rank",
+                       "ms_per_token": e2e_ms / launches}
+    return line
+
+
+def run_tp(args, rank, world, local):
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py measures the CUDA megakernel; no CUDA device is visible")
+    line = measure_split_decode(args.workload, args.weights, args.steps, args.warmup, rank, world, local,
+                                schedule=args.schedule, self_test=args.self_test)
     if rank == 0:
-        peak, peak_src = measured_hbm_peak()
-        kv = kv_bytes_per_position(cfg)
-        weight_bytes = linear_weight_bytes(cfg) * (0.5625 / 2.0 if fp4 else 1.0)
-        total_bytes = sum(weight_bytes + kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
-        launch_ms = elapsed_ms / launches
-        achieved = total_bytes / world / (launch_ms / 1000.0) / 1e9  # per GPU: every rank streams 1/world of the bytes
-        line = {
-            "metric": "decode_tokens_per_s", "value": launches / (elapsed_ms / 1000.0), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 activations and KV, NVFP4 weights" if fp4 else "bf16", "data": "synthetic",
-            "config": {
-                "workload": f"{args.workload} ({args.weights} weights): {'SELF-TEST 2-layer ' if args.self_test else ''}batch-1 greedy decode, "
-                            f"{ctx} cached positions, {ntok} tokens per step",
-                "step": f"{ntok} megakernel launches per rank",
-                "ms_per_token": launch_ms,
-                "parallelism": f"tp{world}" if world > 1 else "single",
-                "attention_partitions_per_kv_head": partitions,
-                "l2": "inputs larger than L2",
-            },
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": total_bytes / world,
-                         "launch_ms": launch_ms, "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "note": "per GPU: total algorithmic bytes / n_gpus over the launch time"},
-            "e2e": {"value": launches / (e2e_ms / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": 4,
-                    "d2h_bytes_per_step": 4 * ntok, "api": "Megakernel.decode on every rank", "ms_per_token": e2e_ms / launches},
-            "gpu_launches": launches, "clocks": clocks, "cpu_baseline": None,
-        }
         print(json.dumps(line), flush=True)
+
+
+PARITY_MODEL = dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                    intermediate_size=8192, vocab_size=4096)
+
+
+def tp_parity_check(rank: int, world: int, local: int) -> dict | None:
+    """Four tokens of a 2-layer model, decoded with the model split over the ranks
+    and, on rank 0, with the whole model on one GPU fed the same tokens.  The
+    split sums in a different order, so hidden state and logits agree to the
+    rounding noise of two layers (NRMSE about 1 %), not bit for bit; the ranks
+    among themselves must be bit-identical."""
+    import torch.distributed as dist
+
+    from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
+    from thor_megakernels_b200.dispatch import make_mk_interpreter
+    from thor_megakernels_b200.generators import MK_Generator
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+    from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+    from thor_megakernels_b200.tp import TensorParallelDecoder
+
+    device = torch.device(f"cuda:{local}")
+    ctx, ntok, first = 19, 4, 77
+    model = LlamaForCausalLM.random_init(LlamaConfig(**PARITY_MODEL), ExtraModelConfig(interleave_rope=True, max_len_override=64),
+                                         seed=3, device=device, generate_on=device)
+    gen = torch.Generator(device=device).manual_seed(21)
+    for cache in model.stacked_kv_cache:
+        cache[:, :, :ctx] = torch.randn(cache[:, :, :ctx].shape, generator=gen, device=device).bfloat16()
+    tp = TensorParallelDecoder(model, rank, world)
+    tokens = tp.decode(first, ntok, ctx)
+    torch.cuda.synchronize(device)
+    tp.mk.status()
+    hidden = tp.schedule.globs.hidden_states.clone()
+    vocab_share = PARITY_MODEL["vocab_size"] // world
+    logits = torch.empty(world * vocab_share, dtype=torch.bfloat16, device=device)
+    dist.all_gather_into_tensor(logits, tp.logits().contiguous())
+    all_hidden = torch.empty(world * hidden.numel(), dtype=torch.bfloat16, device=device)
+    dist.all_gather_into_tensor(all_hidden, hidden)
+    all_tokens = torch.empty(world * ntok, dtype=torch.int32, device=device)
+    dist.all_gather_into_tensor(all_tokens, tokens)
+    identical = all(torch.equal(all_hidden[r * hidden.numel():(r + 1) * hidden.numel()], hidden) and
+                    torch.equal(all_tokens[r * ntok:(r + 1) * ntok], tokens) for r in range(world))
+    out = None
+    if rank == 0:
+        sched = LatencyScheduleBuilder.build(model)
+        tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+        whole = MK_Generator(model, make_mk_interpreter("latency"), sched)
+        fed = [first] + tokens.cpu().tolist()[:-1]
+        whole_tokens = [int(whole.run(torch.tensor([[tok]], device=device), pos_id=ctx + i)) for i, tok in enumerate(fed)]
+        torch.cuda.synchronize(device)
+        g = sched.globs
+
+        def nrmse(a, b):
+            a, b = a.float(), b.float()
+            return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+        out = {"model": "2 layers of the 1B shapes, 4 tokens, split over the ranks vs whole on rank 0 (teacher-forced)",
+               "nrmse_hidden": nrmse(hidden, g.hidden_states), "nrmse_logits": nrmse(logits, g.logits),
+               "tokens_equal": sum(int(a == b) for a, b in zip(tokens.cpu().tolist(), whole_tokens)), "tokens": ntok,
+               "ranks_bit_identical": bool(identical),
+               "ok": bool(identical) and nrmse(hidden, g.hidden_states) <= 0.02 and nrmse(logits, g.logits) <= 0.02}
+    tp.close()
+    dist.barrier()
+    return out
+
+
+def llama8b_records(args, rank, world, local) -> dict | None:
+    """Config-4 figures at this GPU count: bf16 and NVFP4 weight-only."""
+    out = {}
+    steps = max(2, min(args.steps, 6))
+    for weights in ("bf16", "nvfp4"):
+        line = measure_split_decode("llama8b-tp", weights, steps, 3, rank, world, local, schedule=args.schedule,
+                                    self_test=args.self_test, e2e=False)
+        torch.cuda.empty_cache()
+        if rank == 0:
+            out[weights] = {"tokens_per_s": line["value"], "ms_per_token": line["config"]["ms_per_token"],
+                            "per_gpu_roofline_frac": line["roofline"]["frac"], "per_gpu_GBps": line["roofline"]["achieved"],
+                            "attention_partitions_per_kv_head": line["config"]["attention_partitions_per_kv_head"],
+                            "clocks": line["clocks"], "steps": steps, "tokens_per_step": TP_WORKLOADS["llama8b-tp"][2]}
+    if rank != 0:
+        return None
+    out["workload"] = ("llama-3.1-8b-arch batch-1 greedy decode, 8192 cached positions, 64 tokens per step, "
+                       f"{'split over ' + str(world) + ' GPUs (tensor parallel)' if world > 1 else 'one GPU'}")
+    return out
+
+
+def run_headline_split(args, rank, world, local):
+    """N > 1: the headline request with the 1B model split over the N GPUs."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py measures the CUDA megakernel; no CUDA device is visible")
+    parity = tp_parity_check(rank, world, local)
+    torch.cuda.empty_cache()
+    line = measure_split_decode("llama1b-tp", "bf16", args.steps, args.warmup, rank, world, local,
+                                schedule=args.schedule, self_test=args.self_test)
+    torch.cuda.empty_cache()
+    big = None if args.no_8b else llama8b_records(args, rank, world, local)
+    if rank == 0:
+        line["config"]["workload"] = ("llama-3.2-1b-arch bf16 batch-1 greedy decode: 16-token context, 100 tokens (pos 16..115), "
+                                      f"model split over {world} GPUs")
+        line["tp_parity"] = parity
+        line["llama8b_tp"] = big
+        print(json.dumps(line), flush=True)
+
+
+def run_timeline(args, rank, world, local):
+    """One decode step with per-instruction clock stamps; prints, per opcode of a
+    middle layer, when its instructions had their input, how long they streamed
+    and when their output was stored, plus the hand-off gaps between phases."""
+    if rank != 0:
+        return
+    import numpy as np
+
+    from thor_megakernels_b200.runtime import (MK_STEP_EMBED, MK_STEP_RESET_BARRIERS, MK_STEP_TIMINGS, MK_STEP_WRITE_TOKEN,
+                                               Megakernel)
+
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    model, sched = build_gpu_model(device, schedule=args.schedule)
+    g = sched.globs
+    quantized = None
+    if args.weights == "nvfp4":
+        from thor_megakernels_b200.nvfp4 import quantize_model
+
+        quantized = quantize_model(model)
+    mk = Megakernel.from_globals(g, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
+    tok = torch.tensor([17], dtype=torch.int32, device=device)
+    out = torch.zeros(1, dtype=torch.int32, device=device)
+    flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN
+    for _ in range(5):
+        mk.step(args.pos, flags=flags, token_in=tok, token_out=out)
+    torch.cuda.synchronize(device)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    mk.step(args.pos, flags=flags, token_in=tok, token_out=out)
+    e.record()
+    torch.cuda.synchronize(device)
+    plain_ms = s.elapsed_time(e)
+    g.timings.zero_()
+    s.record()
+    mk.step(args.pos, flags=flags | MK_STEP_TIMINGS, token_in=tok, token_out=out)
+    e.record()
+    torch.cuda.synchronize(device)
+    mk.status()
+    stamped_ms = s.elapsed_time(e)
+    T, I = g.timings.cpu().numpy().astype(np.float64), g.instructions.cpu().numpy()
+    mhz = torch.cuda.clock_rate() if hasattr(torch.cuda, "clock_rate") else 1965
+    T = T / float(mhz)  # microseconds since the CTA started
+    ops = I[:, :, 0]
+    names = {1: "qkv", 2: "attention", 3: "attn_merge", 4: "o_proj", 5: "gate_up", 6: "down", 7: "lm_head"}
+    layers = MODEL["num_hidden_layers"]
+    mid = list(range(max(1, layers // 2 - 2), min(layers, layers // 2 + 2)))
+    rows, ends = [], {}
+    for op in (1, 2, 3, 4, 5, 6):
+        per_layer = []
+        for layer in mid:
+            m = (ops == op) & (I[:, :, 1] == layer)
+            if not m.any():
+                continue
+            ready = np.where(op == 2, T[:, :, 45], T[:, :, 49])[m]   # input present (attention: q arrived)
+            last_use, last_store = T[:, :, 52][m], np.where(op in (2, 3), T[:, :, 54], T[:, :, 53])[m]
+            per_sm = m.sum(axis=1)
+            per_layer.append((ready.min(), ready.max(), last_use.min(), last_use.max(), last_store.max(),
+                              float(np.mean(last_use - ready)), int(m.sum()), int(per_sm.max()), int((per_sm > 0).sum())))
+            ends[(op, layer)] = (ready.min(), last_store.max())
+        if per_layer:
+            a = np.array(per_layer, dtype=np.float64)
+            t0 = np.array([ends[(1, layer)][0] for layer in mid])  # relative to the layer's first QKV input
+            rows.append({"op": names[op], "instructions_per_layer": int(a[0, 6]), "sms_used": int(a[0, 8]),
+                         "max_instructions_per_sm": int(a[0, 7]),
+                         "input_ready_us": [round(float(np.mean(a[:, 0] - t0)), 2), round(float(np.mean(a[:, 1] - t0)), 2)],
+                         "last_use_us": [round(float(np.mean(a[:, 2] - t0)), 2), round(float(np.mean(a[:, 3] - t0)), 2)],
+                         "output_stored_us": round(float(np.mean(a[:, 4] - t0)), 2),
+                         "mean_streaming_us": round(float(np.mean(a[:, 5])), 2)})
+    layer_us = float(np.mean([ends[(1, layer + 1)][0] - ends[(1, layer)][0] for layer in mid if (1, layer + 1) in ends]))
+    m7 = ops == 7
+    head = {"input_ready_us": [float(T[:, :, 49][m7].min()), float(T[:, :, 49][m7].max())],
+            "last_use_us": [float(T[:, :, 52][m7].min()), float(T[:, :, 52][m7].max())]}
+    weights_mb = (linear_weight_bytes(MODEL) - 2 * MODEL["vocab_size"] * MODEL["hidden_size"]) / layers / 1e6
+    if args.weights == "nvfp4":
+        weights_mb *= 0.5625 / 2
+    print(json.dumps({"workload": f"one step at position {args.pos}, {args.weights} weights, schedule {args.schedule}",
+                      "ms_plain": plain_ms, "ms_with_stamps": stamped_ms, "layers_averaged": mid,
+                      "layer_period_us": round(layer_us, 2), "layer_weight_MB": round(weights_mb, 1),
+                      "times": "microseconds after the layer's first QKV instruction had its input; [earliest SM, latest SM]",
+                      "per_op": rows, "lm_head": head}), flush=True)
+    if args.dump:
+        np.savez_compressed(args.dump, timings=g.timings.cpu().numpy(), instructions=I)
+
+
+def run_profile_step(args, rank, world, local):
+    """A few bare decode steps and nothing else, so that a profiler sees only
+    megakernel launches.  Prints the mean step time measured with CUDA events."""
+    if rank != 0:
+        return
+    from thor_megakernels_b200.runtime import MK_STEP_EMBED, MK_STEP_RESET_BARRIERS, MK_STEP_WRITE_TOKEN, Megakernel
+
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    if args.arch == "8b":
+        # Llama-3.1-8B layer shapes with a long cache (attention split into slices), few layers to keep a capture small
+        from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
+        from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+        from thor_megakernels_b200.model_types import ExtraModelConfig
+        from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+        cfg = dict(MODEL_8B, num_hidden_layers=args.layers or 4)
+        extra = ExtraModelConfig(interleave_rope=True, max_len_override=args.pos + 16)
+        model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=4, device=device, generate_on=device)
+        gen = torch.Generator(device=device).manual_seed(3)
+        for cache in model.stacked_kv_cache:
+            cache[:, :, :args.pos] = torch.randn(cache[:, :, :args.pos].shape, generator=gen, device=device).bfloat16()
+        sched = make_schedule(model, args.schedule, skip_attn_reduction=args.partitions == 1,
+                              num_attention_partitions=args.partitions)
+        sched.globs.barriers.zero_()
+    else:
+        if args.layers is not None:
+            MODEL.update(num_hidden_layers=args.layers)
+        model, sched = build_gpu_model(device, schedule=args.schedule)
+    quantized = None
+    if args.weights == "nvfp4":
+        from thor_megakernels_b200.nvfp4 import quantize_model
+
+        quantized = quantize_model(model)
+    mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
+    tok = torch.tensor([17], dtype=torch.int32, device=device)
+    out = torch.zeros(1, dtype=torch.int32, device=device)
+    flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    mk.step(args.pos, flags=flags, token_in=tok, token_out=out)
+    torch.cuda.synchronize(device)
+    start.record()
+    for _ in range(args.steps):
+        mk.step(args.pos, flags=flags, token_in=tok, token_out=out)
+    end.record()
+    torch.cuda.synchronize(device)
+    mk.status()
+    print(f"{args.steps} steps at position {args.pos}: {start.elapsed_time(end) / args.steps:.4f} ms/step, token {int(out)}")
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one megakernel launch from an ncu capture
@@ -640,9 +917,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tokens", type=int, default=4, help="decode tokens timed for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="llama1b", choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k"],
-                    help="llama1b: the headline workload (replicas when N > 1); *-tp: one sequence split over the GPUs")
-    ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"], help="weight format of the *-tp workloads")
+    ap.add_argument("--no-8b", action="store_true", help="leave out the nested Llama-3.1-8B record")
+    ap.add_argument("--workload", default="llama1b",
+                    choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k", "timeline", "profile-step"],
+                    help="llama1b: the headline workload (split over the GPUs when N > 1); *-tp: only the split decode")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"], help="weight format (tp, timeline, profile-step)")
+    ap.add_argument("--schedule", default="b200", choices=["b200", "rr", "zz", "wave", "dag"],
+                    help="b200: one SM owns all column slices of its down-projection rows; others: the reference's "
+                         "layout under that assignment policy")
+    ap.add_argument("--pos", type=int, default=60, help="timeline / profile-step: position of the step")
+    ap.add_argument("--layers", type=int, default=None, help="profile-step: shrink the model to this many layers")
+    ap.add_argument("--arch", default="1b", choices=["1b", "8b"], help="profile-step: layer shapes")
+    ap.add_argument("--partitions", type=int, default=18, help="profile-step --arch 8b: attention slices per KV head")
+    ap.add_argument("--dump", default=None, help="timeline: also save the raw stamps to this .npz file")
     ap.add_argument("--self-test", action="store_true",
                     help="2-layer, 4096-token-vocabulary model to exercise this script quickly; not a benchmark")
     args = ap.parse_args()
@@ -656,8 +943,14 @@ def main():
             run_gemv(args, rank, world, local)
         elif args.workload == "llama1b-nvfp4-4k":
             run_long_context(args, rank, world, local)
+        elif args.workload == "timeline":
+            run_timeline(args, rank, world, local)
+        elif args.workload == "profile-step":
+            run_profile_step(args, rank, world, local)
         elif args.workload != "llama1b":
             run_tp(args, rank, world, local)
+        elif world > 1:
+            run_headline_split(args, rank, world, local)
         else:
             run_ours(args, rank, world, local)
     finally:

@@ -136,12 +136,16 @@ typedef struct MkLaunchInfo {
     int32_t resident_ctas_per_sm;
     int32_t queue_len;
     int64_t scratch_bytes;         /* device memory the handle allocated itself */
+    int32_t down_fold_mode;        /* how the attached schedule's down-projection slices meet: 0 folds spread over
+                                    * the SMs, 1 folded by the last slice's SM, 2 every SM folds its own rows */
+    int32_t reserved;
 } MkLaunchInfo;
 
 /* Status words of the last step, written by the device when a bounded wait
  * gives up.  code 0 = clean. */
 typedef struct MkStatus {
-    int32_t code;      /* 0 ok, 1 dependency counter wait, 2 weight-ring wait, 3 partial-buffer wait, 4 unknown opcode */
+    int32_t code;      /* 0 ok, 1 dependency counter wait, 2 weight-ring wait, 3 partial-buffer wait, 4 unknown opcode,
+                        * 5 activation data (tagged cells of another SM or GPU) never arrived; detail = which kind */
     int32_t worker;    /* CTA index */
     int32_t opcode;
     int32_t slot;      /* position in that worker's queue */
@@ -173,6 +177,13 @@ int mk_create(const MkModelDesc *desc, void **handle);
  * int32 [workers, queue_len, 128] device tensors as produced by
  * tensorize_instructions (megakernels/scheduler.py:380-413).  workers must not
  * exceed the device's SM count.  May be called again to swap schedules.
+ * The queues are copied to the host once and every operand the device uses as
+ * an index (opcode, layer, row blocks, column slice, attention slice numbers,
+ * list lengths) is range-checked: MK_ERR_BAD_ARGUMENT names the worker and slot
+ * of the first bad instruction.  Attention slice numbers must stay below
+ * min(32, max_partials).  The lowest layer that appears in the queues reads its
+ * input from hidden_states (or the embedding), so a schedule may cover layers
+ * l..L-1 only (the reference's layer_limit cuts from the other end).
  */
 int mk_set_schedule(void *handle, const int32_t *instructions, int32_t *timings,
                     int32_t workers, int32_t queue_len);
@@ -205,6 +216,10 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
 #define MK_OPT_DOWN_FOLD_LAST     3  /* 1: only the instruction of a row block's last column slice folds the slices into the
                                       * residual stream (chosen automatically for queues whose down-projection
                                       * instructions of a layer are not consecutive); 0: folds spread over all SMs */
+#define MK_OPT_DOWN_FOLD_LOCAL    4  /* 1 (default): where every queue holds all column slices of its down-projection
+                                      * row blocks as consecutive instructions in slice order, the SM adds them to
+                                      * the residual itself (same bf16 sequence as the interpreter, no cells parked
+                                      * for another SM); 0: always fold across SMs */
 #define MK_OPT_MAX_INFLIGHT_TILES 2  /* weight tiles (64 KiB bf16 / 18 KiB NVFP4) one loader keeps in flight */
 #define MK_OPT_EARLY_POLL_SHIFT   1  /* consumers stop watching a dependency counter and poll the data cells
                                       * themselves once it is within target >> shift of its target; 31 = never */
@@ -224,13 +239,16 @@ int mk_set_option(void *handle, int32_t option, int64_t value);
  *
  *   mk_tp_init    allocates this GPU's exchange buffer and returns its CUDA IPC
  *                 handle (MK_TP_HANDLE_BYTES bytes) for the host to all-gather;
- *   mk_tp_connect takes the world's handles in rank order and maps the peers.
+ *   mk_tp_connect takes the world's `count` handles in rank order (count must
+ *                 equal the world given to mk_tp_init) and maps the peers.  It
+ *                 restarts the launch count, so it also clears the handle's
+ *                 hand-off cells: steps made before connecting leave nothing behind.
  *
  * Every rank must then make the same sequence of mk_step calls.
  */
 #define MK_TP_HANDLE_BYTES 64
 int mk_tp_init(void *handle, int32_t rank, int32_t world, int32_t vocab_offset, void *ipc_handle_out);
-int mk_tp_connect(void *handle, const void *ipc_handles);
+int mk_tp_connect(void *handle, const void *ipc_handles, int32_t count);
 
 void mk_destroy(void *handle);
 
@@ -249,9 +267,25 @@ int mk_nvfp4_quantize(const void *input_bf16, void *packed, void *scales, float 
  * dequantise), else bf16 weights in `w`.  Mirrors nv_simt
  * (tools/analysis/nvfp4/primitive.cu:79-96, :112-119) and wo_run
  * (experimental/weight_only_fp4/primitive.cu:78-82); batch is 1..8.
+ *
+ * The call allocates nothing (the reference's per-call entry points borrow all
+ * memory from the caller).  When k > 2048 the K dimension is split over CTAs and
+ * the fp32 partial sums go through `workspace`: device memory of at least
+ * mk_gemv_workspace_bytes(m, k) bytes, 256-byte aligned, owned by the caller.
+ * Calls that may overlap in time (different streams) need different
+ * workspaces; calls on one stream can share one.  workspace may be NULL when
+ * mk_gemv_workspace_bytes returns 0.
+ *
+ * NVFP4 weights: the activations are converted from bf16 to f16 for the tensor
+ * cores (code x block scale is exact in f16).  Values beyond +-65504 are clamped
+ * to +-65504 and magnitudes below 2^-24 flush to zero; between 2^-24 and 2^-14
+ * they keep fewer than bf16's 8 significant bits.  The decode megakernel's
+ * NVFP4 path (MK_WEIGHTS_NVFP4) converts its activations the same way.
  */
+int64_t mk_gemv_workspace_bytes(int32_t m, int32_t k);
 int mk_gemv(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y,
-            int32_t m, int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream);
+            int32_t m, int32_t k, float tensor_scale, int32_t is_packed, int32_t batch,
+            void *workspace, int64_t workspace_bytes, void *stream);
 
 /*
  * mk_gemv without any allocation (no reference counterpart: the reference has

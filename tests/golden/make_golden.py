@@ -2,7 +2,7 @@
 own code (imported unchanged from a checkout of yiannisha/thor-megakernels) on
 this repository's seeded weights.
 
-    python tests/golden/make_golden.py --reference /path/to/thor-megakernels [--case tiny|llama1b|all]
+    python tests/golden/make_golden.py --reference /path/to/thor-megakernels [--case tiny|llama1b|llama1b_layers|all]
 
 What is run from the reference: ``LlamaForCausalLM`` (prefill through its
 PyTorch forward), ``LatencyScheduleBuilder`` + ``assign_to_sms`` +
@@ -268,6 +268,83 @@ def run_case(name: str, cfg_kwargs: dict, max_len: int, prompt_len: int, ntok: i
           f"oracle identical: {identical}", flush=True)
 
 
+def run_layers_case(name: str, cfg_kwargs: dict, max_len: int, prompt_len: int, steps: int):
+    """Per-layer record of the reference interpreter's residual stream: for each
+    of the first ``steps`` decode steps, the hidden state entering every layer,
+    the layer's q / attn_out / silu_out, its output and its appended K/V rows.
+    A layer can then be run alone from the reference's own input, which pins it
+    at the stated tolerance without the rounding noise of the layers before it."""
+    from megakernels.demos.latency.python_vm import INSTRUCTION_TO_SOLVER as REF_SOLVERS
+    from megakernels.demos.latency.scheduler import LatencyScheduleBuilder as RefBuilder
+    from megakernels.model_types import BatchState as RefBatch
+    from megakernels.python_vm import interpret_with_pyvm as ref_interpret
+
+    from oracle import pyvm as mine_vm
+    from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
+    from thor_megakernels_b200.model_types import BatchState
+
+    mine, ref = build_pair(cfg_kwargs, max_len, seed=0)
+    ref_sched = RefBuilder.build(ref)
+    my_sched = LatencyScheduleBuilder.build(mine)
+    prompt = torch.randint(0, cfg_kwargs["vocab_size"], (1, prompt_len), generator=torch.Generator().manual_seed(1))
+    pos = torch.arange(prompt_len)[None]
+    out = ref(RefBatch(input_ids=prompt, position_ids=pos, seq_len=prompt_len))
+    mine(BatchState(input_ids=prompt, position_ids=pos, seq_len=prompt_len))
+    token = int(out.output_ids[:, -1])
+    g, mg = ref_sched.globs, my_sched.globs
+    layers = cfg_kwargs["num_hidden_layers"]
+    by_layer = [[] for _ in range(layers)]
+    tail = []
+    for ins in ref_sched.get_linear_instructions():
+        (by_layer[ins.layer_idx] if hasattr(ins, "layer_idx") else tail).append(ins)
+    my_by_layer = [[] for _ in range(layers)]
+    my_tail = []
+    for ins in my_sched.get_linear_instructions():
+        (my_by_layer[ins.layer_idx] if hasattr(ins, "layer_idx") else my_tail).append(ins)
+    arrays = {"prefill_k": u16(ref.stacked_kv_cache[0][:, 0, :prompt_len]),
+              "prefill_v": u16(ref.stacked_kv_cache[1][:, 0, :prompt_len])}
+    tokens, identical = [token], True
+    keep = {k: [] for k in ("layer_in", "q", "attn_out", "silu_out", "layer_out", "k_rows", "v_rows")}
+    for step in range(steps):
+        pos_id = prompt_len + step
+        inp = torch.tensor([[tokens[-1]]])
+        emb = ref.model.embed_tokens(RefBatch(input_ids=inp))
+        g.hidden_states[:] = emb.hidden_states
+        g.barriers.zero_()
+        g.pos_id = pos_id
+        mg.hidden_states[:] = mine.model.embed_tokens(BatchState(input_ids=inp)).hidden_states
+        mg.barriers.zero_()
+        mg.pos_id = pos_id
+        rec = {k: [] for k in keep}
+        for layer in range(layers):
+            rec["layer_in"].append(u16(g.hidden_states))
+            ref_interpret(g, by_layer[layer], REF_SOLVERS)
+            mine_vm.interpret_with_pyvm(mg, my_by_layer[layer])
+            for n in ("hidden_states", "post_ln_rope_q", "attn_out", "silu_out"):
+                identical &= torch.equal(getattr(g, n), getattr(mg, n))
+            rec["q"].append(u16(g.post_ln_rope_q))
+            rec["attn_out"].append(u16(g.attn_out))
+            rec["silu_out"].append(u16(g.silu_out))
+            rec["layer_out"].append(u16(g.hidden_states))
+            rec["k_rows"].append(u16(ref.stacked_kv_cache[0][layer, 0, pos_id]))
+            rec["v_rows"].append(u16(ref.stacked_kv_cache[1][layer, 0, pos_id]))
+        ref_interpret(g, tail, REF_SOLVERS)
+        emb.hidden_states = g.hidden_states
+        tokens.append(int(ref.lm_head(emb).output_ids))
+        for k in keep:
+            keep[k].append(np.stack(rec[k]))
+        print(f"[{name}] step {step} token {tokens[-1]} identical={identical}", flush=True)
+    for k in keep:
+        arrays[k] = np.stack(keep[k])   # [steps, layers, ...]
+    arrays["tokens"] = np.asarray(tokens, dtype=np.int32)
+    assert identical, "oracle/pyvm.py is not bit-identical to the reference's python_vm, layer by layer"
+    meta = {"case": name, "config": cfg_kwargs, "max_len": max_len, "prompt_len": prompt_len, "steps": steps,
+            "oracle_bit_identical": bool(identical), "torch": torch.__version__}
+    np.savez_compressed(HERE / f"{name}.npz", **arrays)
+    (HERE / f"{name}.json").write_text(json.dumps(meta, indent=1))
+    print(f"[{name}] wrote {name}.npz ({(HERE / (name + '.npz')).stat().st_size / 1e6:.2f} MB)", flush=True)
+
+
 CASES = {
     # two layers, small vocabulary: every buffer of every step is kept
     "tiny": dict(cfg_kwargs=dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8,
@@ -291,6 +368,10 @@ def main():
     for name, spec in CASES.items():
         if args.case in ("all", name):
             run_case(name, **spec)
+    if args.case in ("all", "llama1b_layers"):
+        # same model, prompt and token stream as the llama1b case
+        spec = CASES["llama1b"]
+        run_layers_case("llama1b_layers", spec["cfg_kwargs"], spec["max_len"], spec["prompt_len"], steps=3)
 
 
 if __name__ == "__main__":

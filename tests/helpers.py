@@ -37,6 +37,10 @@ def build_schedule(model, mode: str = "rr", **kwargs):
     from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
     from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
 
+    if mode == "b200":  # rows-together down projection + row-keeping round robin
+        from thor_megakernels_b200.demos.latency.scheduler import build_b200_schedule
+
+        return build_b200_schedule(model, **kwargs)
     sched = LatencyScheduleBuilder.build(model, **kwargs)
     tensorize_instructions(sched.globs, assign_to_sms(mode, schedule=sched))
     return sched

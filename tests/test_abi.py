@@ -48,7 +48,11 @@ def test_bad_arguments_are_rejected_without_a_device():
     assert lib.mk_create(C.byref(desc), C.byref(handle)) == _lib.MK_ERR_UNSUPPORTED
     assert lib.mk_step(None, 0, 0, None, None, None) == _lib.MK_ERR_BAD_ARGUMENT
     assert lib.mk_query(None, None) == _lib.MK_ERR_BAD_ARGUMENT
-    assert lib.mk_gemv(None, None, None, None, None, 16, 32, 1.0, 0, 1, None) != 0
+    assert lib.mk_gemv(None, None, None, None, None, 16, 32, 1.0, 0, 1, None, 0, None) != 0
+    # split-K scratch is the caller's: size query only, no device needed
+    assert lib.mk_gemv_workspace_bytes(8192, 2048) == 0
+    assert lib.mk_gemv_workspace_bytes(2048, 8192) == 512 + 4 * 8 * 2048 * 4
+    assert lib.mk_tp_connect(None, None, 2) == _lib.MK_ERR_BAD_ARGUMENT
     assert lib.mk_nvfp4_quantize(None, None, None, None, 1, 16, 1.0, None) != 0
     lib.mk_destroy(None)
 

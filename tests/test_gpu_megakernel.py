@@ -108,10 +108,13 @@ def test_tiny_matches_live_oracle_and_fused_loop(tiny):
     assert_close("logits", sched.globs.logits, cpu_sched.globs.logits)
 
 
-@pytest.mark.parametrize("mode", ["zz", "wave", "dag"])
+@pytest.mark.parametrize("mode", ["zz", "wave", "dag", "b200"])
 def test_tiny_other_assignment_policies(tiny, mode):
     """Any valid queue assignment gives bit-identical results: the arithmetic
-    does not depend on which SM runs an instruction."""
+    does not depend on which SM runs an instruction.  ``b200`` also changes how
+    the down projection is cut (one SM owns all column slices of its rows and
+    folds them itself); the slices are still added in slice order with a bf16
+    rounding each, so the bits stay the same."""
     meta, arrays, model = tiny
     n = load_prefill(model, arrays)
     tok = torch.tensor([[int(arrays["tokens"][0])]], device="cuda")
@@ -124,6 +127,15 @@ def test_tiny_other_assignment_policies(tiny, mode):
     torch.cuda.synchronize()
     for k, v in want.items():
         assert torch.equal(getattr(sched.globs, k), v), k
+    if mode == "b200":
+        from thor_megakernels_b200.runtime import Megakernel
+
+        mk = Megakernel.from_globals(sched.globs)
+        assert mk.query()["down_fold_mode"] == 2, "the b200 layout must be recognised as locally foldable"
+        mk.close()
+        mk = Megakernel.from_globals(ref_sched.globs)
+        assert mk.query()["down_fold_mode"] == 0
+        mk.close()
 
 
 @pytest.mark.parametrize("stop_after_op,layer_limit", [("qkv", 1), ("partial", 1), ("oproj", 1), ("upgate", 1), ("downproj", 1), (None, 1)])
@@ -447,6 +459,7 @@ def test_llama8b_shapes_two_layers():
         want = pyvm.pyvm_step(cpu_model, cpu_sched, cpu_sched.get_linear_instructions(), torch.tensor([[token]]), pos)
         with exact_matvecs():
             pyvm.pyvm_step(cpu_exact, exact_sched, exact_sched.get_linear_instructions(), torch.tensor([[token]]), pos)
+        token_fed = token
         got = mk_gen.run(torch.tensor([[token]], device="cuda"), pos_id=pos)
         torch.cuda.synchronize()
         for name in ("post_ln_rope_q", "attn_out", "silu_out", "hidden_states", "logits"):
@@ -461,3 +474,10 @@ def test_llama8b_shapes_two_layers():
             top2 = torch.topk(cpu_sched.globs.logits.float(), 2).values
             assert float(top2[0] - top2[1]) <= 0.125
         token = int(want)
+    # the b200 layout (two row blocks and seven column slices per SM, folded locally): same bits as the reference layout
+    want_bits = {name: getattr(sched.globs, name).clone() for name in ("hidden_states", "logits", "silu_out")}
+    local = build_schedule(model, "b200")
+    _mk_generator(model, local).run(torch.tensor([[token_fed]], device="cuda"), pos_id=ctx + 1)
+    torch.cuda.synchronize()
+    for name, bits in want_bits.items():
+        assert torch.equal(getattr(local.globs, name), bits), name

@@ -66,6 +66,40 @@ def test_weight_only_gemv(rows, k, batch):
     assert_close("bf16 gemv", got_bf, want_bf)
 
 
+def test_weight_only_gemv_activation_range():
+    """The NVFP4 GEMV feeds the tensor cores f16 activations.  Magnitudes around
+    1e4 (inside f16's range) must match the oracle like any other input; values
+    beyond 65504 are clamped to it rather than turning into infinities; tiny
+    values lose precision but only in proportion to their (negligible) size."""
+    from thor_megakernels_b200.nvfp4 import gemv, quantize_weight
+
+    torch.manual_seed(6)
+    rows, k = 512, 2048
+    w = (torch.randn(rows, k) * 0.02).bfloat16()
+    q = quantize_weight(w.cuda())
+    dq = torch.from_numpy(oracle.dequantize(q.packed.cpu().numpy(), q.scales.cpu().numpy(), q.tensor_scale)).double()
+    # large but representable
+    x = (torch.randn(1, k) * 1e4).bfloat16()
+    want = (dq @ x.double().T).T.float().bfloat16().float()
+    got = gemv(q, x.cuda()).float().cpu()
+    assert torch.isfinite(got).all()
+    assert rel_l2(got, want) <= 1e-3
+    # beyond f16: the result is that of the clamped activations, and finite
+    x_big = x.clone()
+    x_big[0, ::7] = 3.0e5
+    x_big[0, 3::11] = -2.0e6
+    got = gemv(q, x_big.cuda()).float().cpu()
+    want = (dq @ x_big.double().clamp(-65504, 65504).T).T.float().bfloat16().float()
+    assert torch.isfinite(got).all()
+    assert rel_l2(got, want) <= 1e-3
+    # tiny values next to ordinary ones: absolute error stays at the ordinary values' rounding level
+    x_small = torch.randn(1, k).bfloat16()
+    x_small[0, ::2] = 1e-6
+    want = (dq @ x_small.double().T).T.float().bfloat16().float()
+    got = gemv(q, x_small.cuda()).float().cpu()
+    assert rel_l2(got, want) <= 1e-3
+
+
 def test_gemv_rejects_bad_shapes():
     from thor_megakernels_b200.nvfp4 import gemv, quantize_weight
 

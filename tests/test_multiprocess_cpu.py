@@ -16,7 +16,9 @@ import bench
 rank, world, local = bench.dist_setup(2)
 bench.barrier(world)
 slowest = bench.max_over_ranks(10.0 + rank, world)
-print(json.dumps(dict(rank=rank, world=world, slowest=slowest)), flush=True)
+# one file per rank: two ranks printing to one pipe can interleave their lines
+with open(os.path.join({out!r}, f"rank{{rank}}.json"), "w") as fh:
+    json.dump(dict(rank=rank, world=world, slowest=slowest), fh)
 import torch.distributed as dist
 dist.destroy_process_group()
 """
@@ -24,7 +26,7 @@ dist.destroy_process_group()
 
 def test_two_gloo_ranks_agree_on_the_slowest_time(tmp_path):
     script = tmp_path / "worker.py"
-    script.write_text(WORKER.format(root=str(ROOT)))
+    script.write_text(WORKER.format(root=str(ROOT), out=str(tmp_path)))
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
     import socket
 
@@ -36,7 +38,7 @@ def test_two_gloo_ranks_agree_on_the_slowest_time(tmp_path):
          "127.0.0.1", "--master-port", str(port), str(script)],
         capture_output=True, text=True, env=env, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
-    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    lines = [json.loads((tmp_path / f"rank{r}.json").read_text()) for r in range(2)]
     assert sorted(l["rank"] for l in lines) == [0, 1]
     assert all(l["world"] == 2 and l["slowest"] == 11.0 for l in lines)
 

@@ -26,6 +26,7 @@ MK_OPT_WAIT_BUDGET_CYCLES = 0
 MK_OPT_EARLY_POLL_SHIFT = 1
 MK_OPT_MAX_INFLIGHT_TILES = 2
 MK_OPT_DOWN_FOLD_LAST = 3
+MK_OPT_DOWN_FOLD_LOCAL = 4
 
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1
@@ -33,7 +34,7 @@ MK_WEIGHTS_NVFP4 = 1
 EXPORTED_SYMBOLS = [
     "mk_last_error", "mk_create", "mk_set_schedule", "mk_step", "mk_query", "mk_status",
     "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
-    "mk_gemv_static", "mk_tp_init", "mk_tp_connect",
+    "mk_gemv_static", "mk_tp_init", "mk_tp_connect", "mk_gemv_workspace_bytes",
 ]
 
 
@@ -69,7 +70,7 @@ class MkLaunchInfo(C.Structure):
         "cooperative_launch", "physical_sms", "resident_worker_capacity", "active_workers", "threads_per_cta",
         "consumer_warps", "registers_per_thread", "local_bytes_per_thread", "static_smem_bytes",
         "dynamic_smem_bytes", "stage_count", "stage_bytes", "resident_ctas_per_sm", "queue_len",
-    )] + [("scratch_bytes", C.c_int64)]
+    )] + [("scratch_bytes", C.c_int64), ("down_fold_mode", C.c_int32), ("reserved", C.c_int32)]
 
 
 class MkStatus(C.Structure):
@@ -108,15 +109,17 @@ def load() -> C.CDLL:
     lib.mk_destroy.argtypes = [vp]
     lib.mk_destroy.restype = None
     lib.mk_nvfp4_quantize.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
-    lib.mk_gemv.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
-    lib.mk_gemv_static.argtypes = lib.mk_gemv.argtypes
+    lib.mk_gemv.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp, C.c_int64, vp]
+    lib.mk_gemv_static.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
+    lib.mk_gemv_workspace_bytes.argtypes = [i32, i32]
     lib.mk_tp_init.argtypes = [vp, i32, i32, i32, vp]
-    lib.mk_tp_connect.argtypes = [vp, vp]
+    lib.mk_tp_connect.argtypes = [vp, vp, i32]
     lib.mk_abi_sizeof.argtypes = [i32]
     lib.mk_set_option.argtypes = [vp, i32, C.c_int64]
     for name in EXPORTED_SYMBOLS:
-        if name not in ("mk_last_error", "mk_destroy"):
+        if name not in ("mk_last_error", "mk_destroy", "mk_gemv_workspace_bytes"):
             getattr(lib, name).restype = C.c_int
+    lib.mk_gemv_workspace_bytes.restype = C.c_int64
     return lib
 
 

@@ -18,7 +18,7 @@ SOURCES = ["megakernel.cu", "nvfp4.cu", "gemv.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fPIC",
 ]
 
 
@@ -40,18 +40,36 @@ def is_stale() -> bool:
 def build_library(force: bool = False, verbose: bool = False) -> Path:
     if not force and not is_stale():
         return LIBRARY
-    sources = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
+    sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
+    nvcc = find_nvcc()
     # Build beside the target and rename: several ranks may find the library stale at the same moment,
-    # and none of them must ever load a half-written file.
-    scratch = LIBRARY.with_name(f"{LIBRARY.name}.{os.getpid()}.tmp")
-    cmd = [find_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(scratch), *sources]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        scratch.unlink(missing_ok=True)
-        raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
-    os.replace(scratch, LIBRARY)
+    # and none of them must ever load a half-written file.  Sources compile side by side.
+    tag = f"{os.getpid()}.tmp"
+    objects = [PACKAGE_DIR / f"{src.stem}.{tag}.o" for src in sources]
+    scratch = LIBRARY.with_name(f"{LIBRARY.name}.{tag}")
+    procs = [(subprocess.Popen([nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", str(src), "-o", str(obj)],
+                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True), src)
+             for src, obj in zip(sources, objects)]
+    logs, failed = [], []
+    for proc, src in procs:
+        out, _ = proc.communicate()
+        logs.append(out)
+        if proc.returncode != 0:
+            failed.append(f"{src.name}:\n{out}")
+    try:
+        if failed:
+            raise RuntimeError("nvcc failed:\n" + "\n".join(failed))
+        link = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(scratch),
+                               *map(str, objects)], capture_output=True, text=True)
+        if link.returncode != 0:
+            scratch.unlink(missing_ok=True)
+            raise RuntimeError(f"link failed:\n{link.stdout}\n{link.stderr}")
+        os.replace(scratch, LIBRARY)
+    finally:
+        for obj in objects:
+            obj.unlink(missing_ok=True)
     if verbose:
-        print(proc.stderr)
+        print("\n".join(logs))
     return LIBRARY
 
 

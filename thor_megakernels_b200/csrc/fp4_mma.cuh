@@ -66,9 +66,12 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
     return d;
 }
 
-// Two bf16 (packed) -> two f16 (packed).  Exact for 2^-14 <= |x| < 65520.
+// Two bf16 (packed) -> two f16 (packed).  Exact for 2^-14 <= |x| <= 65504;
+// larger magnitudes are clamped to +-65504 (the largest finite f16) instead of
+// becoming infinite, smaller ones lose bits and flush to zero below 2^-24.
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
-    const __half2 h = __floats2half2_rn(bf16_lo(v), bf16_hi(v));
+    const float lo = fminf(fmaxf(bf16_lo(v), -65504.f), 65504.f), hi = fminf(fmaxf(bf16_hi(v), -65504.f), 65504.f);
+    const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 

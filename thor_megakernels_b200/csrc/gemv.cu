@@ -128,54 +128,31 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_mma_kernel(
     }
 }
 
-// Scratch of the split-K path, allocated once per device on first use and kept
-// for the life of the process.
-struct GemvScratch {
-    float *partial = nullptr;
-    int *tickets = nullptr;
-    size_t partial_floats = 0;
-    int ticket_count = 0;
-};
-static GemvScratch g_scratch[64];
+// Split-K scratch of mk_gemv lives in a caller-owned workspace: row-block
+// tickets (ints, padded to 256 bytes) followed by the fp32 partial sums.
+static size_t gemv_ticket_bytes(int m) {
+    const size_t row_blocks = (size_t)(m + kGemvRows - 1) / kGemvRows;
+    return (row_blocks * sizeof(int) + 255) & ~size_t(255);
+}
 
-static cudaError_t gemv_scratch(int device, size_t floats, int tickets, GemvScratch **out) {
-    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
-    GemvScratch &sc = g_scratch[device];
-    if (sc.partial_floats < floats) {
-        if (sc.partial) cudaFree(sc.partial);
-        sc.partial = nullptr; sc.partial_floats = 0;
-        cudaError_t e = cudaMalloc(&sc.partial, floats * sizeof(float));
-        if (e != cudaSuccess) return e;
-        sc.partial_floats = floats;
-    }
-    if (sc.ticket_count < tickets) {
-        if (sc.tickets) cudaFree(sc.tickets);
-        sc.tickets = nullptr; sc.ticket_count = 0;
-        cudaError_t e = cudaMalloc(&sc.tickets, tickets * sizeof(int));
-        if (e != cudaSuccess) return e;
-        e = cudaMemset(sc.tickets, 0, tickets * sizeof(int));
-        if (e != cudaSuccess) return e;
-        sc.ticket_count = tickets;
-    }
-    *out = &sc;
-    return cudaSuccess;
+size_t gemv_workspace_bytes(int m, int k) {
+    const int chunks = (k + kGemvChunk - 1) / kGemvChunk;
+    if (chunks <= 1) return 0;
+    return gemv_ticket_bytes(m) + (size_t)chunks * kGemvMaxBatch * (size_t)m * sizeof(float);
 }
 
 cudaError_t launch_gemv_mma(const void *w, const void *packed, const void *scales, const void *x, void *y, int m, int k,
-                            float ts, int is_packed, int batch, cudaStream_t stream) {
+                            float ts, int is_packed, int batch, void *workspace, cudaStream_t stream) {
     const int row_blocks = (m + kGemvRows - 1) / kGemvRows;
     const int chunks = (k + kGemvChunk - 1) / kGemvChunk;
     float *partial = nullptr;
     int *tickets = nullptr;
     if (chunks > 1) {
-        int device = 0;
-        cudaError_t e = cudaGetDevice(&device);
+        tickets = reinterpret_cast<int *>(workspace);
+        partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) + gemv_ticket_bytes(m));
+        // the tickets count arrivals per row block and must start at zero; the partial sums are written before they are read
+        cudaError_t e = cudaMemsetAsync(tickets, 0, row_blocks * sizeof(int), stream);
         if (e != cudaSuccess) return e;
-        GemvScratch *sc = nullptr;
-        e = gemv_scratch(device, (size_t)chunks * kGemvMaxBatch * m, row_blocks, &sc);
-        if (e != cudaSuccess) return e;
-        partial = sc->partial;
-        tickets = sc->tickets;
     }
     const dim3 grid(row_blocks * chunks), block(kGemvWarps * 32);
     if (is_packed)

@@ -79,6 +79,7 @@ constexpr int kDownGroup = 4;     // row blocks whose slices the merging storer 
 constexpr int kFetchPerLane = 6;  // cells per lane in that fetch
 constexpr int kMaxRanks = 8;                              // tensor-parallel ranks
 constexpr int kTaggedPartials = 32;                       // attention slices per KV head the scratch can hold
+constexpr int kLocalBlocks = 8;   // row blocks of one down-projection instruction when its SM folds the slices itself
 
 // timing slots (reference include/util.cuh:225-256)
 constexpr int kEvLoaderStart = 5, kEvStorerStart = 9, kEvConsumerStart = 11;
@@ -107,7 +108,9 @@ struct Params {
     int down_width;   // columns of one down-projection slice (multiple of 256, at most 2048)
     int down_slices;  // inter / down_width
     int down_owner_last;  // 1: the last slice's instruction folds a row block at once (see fold_down_blocks)
+    int down_local;       // 1: every queue holds all column slices of its row blocks, in slice order: the SM folds them itself
     int down_total;   // (hidden / 16) * down_slices
+    int first_layer;  // lowest layer the schedule touches: its input is the step input, not the previous layer's cells
     // weights
     const bf16 *qkv_w, *attn_norm_w, *o_w, *mlp_norm_w, *up_w, *gate_w, *down_w, *lm_norm_w, *lm_w, *embed_w;
     // NVFP4 weights: per-layer tables in device memory (null for bf16 models)
@@ -161,6 +164,7 @@ struct __align__(128) Smem {
     float red[2][kConsumerWarps];
     __align__(16) bf16 xbuf[2 * kChunkCols];  // normalised activations, re-read in the MMA operand layout
     float down_parts[kDownGroup][kMaxDownSlices][kBlockRows];  // down-projection slices of the blocks being merged
+    float down_acc[kLocalBlocks][kBlockRows];                  // running residual / sum of the rows an SM folds by itself
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
     uint64_t pfull[kPartialBufs];
@@ -363,6 +367,12 @@ __device__ __forceinline__ unsigned long long *xchg_token(const Params &p, int g
 
 __device__ __forceinline__ const int *instruction_at(const Params &p, int slot) {
     return p.instructions + ((size_t)blockIdx.x * p.queue_len + slot) * kInstrWords;
+}
+
+// Pulls the next instruction's 128-byte line towards this SM while the current
+// instruction runs, so that reading its opcode later does not cost a trip to L2.
+__device__ __forceinline__ void prefetch_instruction(const Params &p, int slot) {
+    if (slot < p.queue_len) asm volatile("prefetch.global.L1 [%0];" ::"l"(instruction_at(p, slot)));
 }
 
 __device__ __forceinline__ void stamp(const Params &p, int slot, int event, long long t_start) {
@@ -590,7 +600,8 @@ __device__ __forceinline__ void consumer_wait(const Params &p, Smem &s, int ctid
                                               int opcode, int slot) {
     // The counter is a hint: once most producers are done, the threads go on to
     // poll the cells they need, which saves the counter's round trip for the last ones.
-    if (ctid == 0) wait_counter(p, s, ctr, expected - (expected >> p.early_shift), opcode, slot);
+    const int target = expected - (expected >> p.early_shift);
+    if (ctid == 0 && target > 0) wait_counter(p, s, ctr, target, opcode, slot);  // target 0: not even one look at the counter
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
 }
 
@@ -1087,18 +1098,19 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
     for (int slot = 0; slot < p.queue_len; ++slot) {
         const int *ins = instruction_at(p, slot);
         const int op = __ldg(ins);
+        if (lane == 0) prefetch_instruction(p, slot + 1);
         if (op == 0) continue;
         if (ctid == 0) stamp(p, slot, kEvConsumerStart, t_start);
         uint4 x[NCH][8];
         switch (op) {
         case 1: {
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
-            if (layer > 0) {
+            if (layer != p.first_layer) {
                 if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
                 consumer_wait(p, s, ctid, counter(p, layer - 1, 5, 0), p.down_total, op, slot);
                 if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
             }
-            load_normed<NCH, FP4>(p, s, ctid, st.norm_toggle, tag, layer == 0 ? step_input : nullptr,
+            load_normed<NCH, FP4>(p, s, ctid, st.norm_toggle, tag, layer == p.first_layer ? step_input : nullptr,
                                   p.t_hidden + (size_t)(layer - 1) * (p.hidden / 2),
                                   p.attn_norm_w + (size_t)layer * p.hidden, x, op, slot);
             if (ctid == 0) stamp(p, slot, kEvFirstUse, t_start);
@@ -1138,6 +1150,44 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
         }
         case 6: {
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
+            if (p.down_local) {
+                // This queue holds the instructions of all column slices of rows
+                // [b0*16, b1*16) in the next down_slices slots (checked when the schedule
+                // was attached).  They are run as one piece: while the tiles of slice r
+                // go through the tensor cores, the cells of slice r+1 of the SiLU product
+                // are already on their way from L2, so the SM pays the wait for its input
+                // once instead of once per slice.  Loader and storer still see one
+                // instruction per slice.
+                const int S = p.down_slices, width = p.down_width;
+                const int t = lane & 3;
+                const bool has_cols = ctid * 8 < width;  // narrower slices leave the upper threads without columns
+                const unsigned long long *silu = p.t_silu + ((size_t)layer * p.inter) / 2 + (ctid * 8) / 2;
+                uint4 mine = make_uint4(0u, 0u, 0u, 0u), nxt = make_uint4(0u, 0u, 0u, 0u);
+                if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
+                named_barrier_sync(kConsumerBarrier, kConsumerThreads);  // everybody is done with the previous operand in xbuf
+                if (has_cols) load8_wait(p, s, silu, tag, mine, op, slot);
+                if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
+                for (int r = 0; r < S; ++r) {
+                    if (ctid == 0 && r > 0) stamp(p, slot + r, kEvConsumerStart, t_start);
+                    bf16 *half = s.xbuf + (r & 1) * kChunkCols;
+                    *reinterpret_cast<uint4 *>(&half[ctid * 8]) = mine;
+                    named_barrier_sync(kConsumerBarrier, kConsumerThreads);
+                    uint4 xs[1][8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) xs[0][j] = operand_convert<FP4>(lds128(&half[operand_column<FP4>(cw, t, j)]));
+                    bool ok = true;
+                    if (r + 1 < S && has_cols) ok = try_load8(silu + ((size_t)(r + 1) * width) / 2, tag, nxt);
+                    if (ctid == 0) stamp(p, slot + r, kEvFirstUse, t_start);
+                    for (int b = b0; b < b1; ++b) consume_block<1, FP4>(p, s, st, lane, cw, xs, op, slot + r, 1, width);
+                    if (ctid == 0) stamp(p, slot + r, kEvLastUse, t_start);
+                    if (r + 1 < S) {
+                        if (!ok) load8_wait(p, s, silu + ((size_t)(r + 1) * width) / 2, tag, nxt, op, slot + r + 1);
+                        mine = nxt;
+                    }
+                }
+                slot += S - 1;  // the slices' instructions have been consumed
+                continue;
+            }
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             // only the gate/up rows of this 2048-column slice have to be ready
             consumer_wait(p, s, ctid, counter(p, layer, kSliceCounterRow, red), p.down_width / kBlockRows, op, slot);
@@ -1383,6 +1433,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
     for (int slot = 0; slot < p.queue_len; ++slot) {
         const int *ins = instruction_at(p, slot);
         const int op = __ldg(ins);
+        if (lane == 0) prefetch_instruction(p, slot + 1);
         if (op == 0) continue;
         if (lane == 0) stamp(p, slot, kEvStorerStart, t_start);
         switch (op) {
@@ -1451,7 +1502,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // layer's output.  It is upstream of this instruction, so it is fetched
             // (and waited for) before the sums arrive.
             auto residual = [&](int row) {
-                if (layer == 0) return ldcg_bf16(step_input + row);
+                if (layer == p.first_layer) return ldcg_bf16(step_input + row);
                 const uint32_t pr = load1_wait(p, s, p.t_hidden + ((size_t)(layer - 1) * p.hidden + row) / 2, tag, op, slot);
                 return (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
             };
@@ -1462,7 +1513,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                     const float y = collect_block(p, s, st, lane, op, slot) * ts;
                     if (writer && !aborted(s)) tp_push(p, tag, 0, layer, b * kBlockRows + lane, y);
                 }
-                tp_fold_blocks(p, s, lane, tag, 0, layer, b0, b1, 1, layer == 0 ? step_input : nullptr,
+                tp_fold_blocks(p, s, lane, tag, 0, layer, b0, b1, 1, layer == p.first_layer ? step_input : nullptr,
                                p.t_hidden + (size_t)(layer > 0 ? layer - 1 : 0) * (p.hidden / 2),
                                p.t_resid + (size_t)layer * (p.hidden / 2), op, slot);
                 publish(p, s, lane, counter(p, layer, 3, 0), b1 - b0);
@@ -1515,6 +1566,49 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // step (fold_down_blocks), run once this SM has parked all of its slices
             // of the layer.
             const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
+            if (p.down_local) {
+                // This SM holds every column slice of rows [b0*16, b1*16) as consecutive
+                // instructions in slice order, so the interpreter's sequential
+                // `hidden += bf16(slice sum)` (python_vm.py:59-80) runs right here: no cells
+                // parked for another SM, no second hand-off.  The running value of a row
+                // stays in shared memory between the slices' instructions.
+                const bool last = red == p.down_slices - 1;
+                const bool sum_fp32 = p.model_numerics || p.tp_world > 1;  // slices added in fp32, rounded once at the end
+                for (int b = b0; b < b1; ++b) {
+                    float h = 0.f;
+                    if (red == 0 && writer && !sum_fp32) {
+                        // residual entering the MLP block: written by the output projection long ago
+                        const int row = b * kBlockRows + lane;
+                        const uint32_t pr = load1_wait(p, s, p.t_resid + ((size_t)layer * p.hidden + row) / 2, tag, op, slot);
+                        h = (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
+                    }
+                    const float y = collect_block(p, s, st, lane, op, slot);
+                    if (writer) {
+                        if (red != 0) h = s.down_acc[b - b0][lane];
+                        h = sum_fp32 ? h + y : round_bf16(h + round_bf16(y));
+                        s.down_acc[b - b0][lane] = h;
+                    }
+                    if (!last) continue;
+                    if (p.tp_world > 1) {
+                        if (writer && !aborted(s)) tp_push(p, tag, 1, layer, b * kBlockRows + lane, h * down_scale(p, layer));
+                        continue;
+                    }
+                    if (sum_fp32 && writer) {
+                        const int row = b * kBlockRows + lane;
+                        const uint32_t pr = load1_wait(p, s, p.t_resid + ((size_t)layer * p.hidden + row) / 2, tag, op, slot);
+                        const float r = (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
+                        h = round_bf16(r + round_bf16(h * down_scale(p, layer)));
+                    }
+                    const float h_next = __shfl_xor_sync(0xffffffffu, h, 1);
+                    if (pair_writer && !aborted(s))
+                        st_tagged(p.t_hidden + ((size_t)layer * p.hidden + b * kBlockRows + lane) / 2, pack_bf16x2(h, h_next), tag);
+                }
+                if (last && p.tp_world > 1)
+                    tp_fold_blocks(p, s, lane, tag, 1, layer, b0, b1, 1, nullptr, p.t_resid + (size_t)layer * (p.hidden / 2),
+                                   p.t_hidden + (size_t)layer * (p.hidden / 2), op, slot);
+                publish(p, s, lane, counter(p, layer, 5, 0), b1 - b0);
+                break;
+            }
             unsigned long long *mine = p.t_down + ((size_t)layer * p.down_slices + red) * p.hidden;
             for (int b = b0; b < b1; ++b) {
                 const float y = collect_block(p, s, st, lane, op, slot);
@@ -1706,6 +1800,8 @@ struct Handle {
     size_t xchg_bytes = 0;
     int fold_last_detected = 0;        // some queue holds a layer's down-projection instructions apart
     int fold_last_forced = 0;          // MK_OPT_DOWN_FOLD_LAST
+    int fold_local_detected = 0;       // every queue keeps the slices of its row blocks together, in order
+    int fold_spread_forced = 0;        // MK_OPT_DOWN_FOLD_LOCAL = 0: use the cross-SM fold even where the local one applies
     int tp_world_pending = 0;          // set by mk_tp_init, becomes params.tp_world in mk_tp_connect
     void *peer_xchg[kMaxRanks] = {};   // peers' buffers opened over CUDA IPC
 };
@@ -1916,17 +2012,76 @@ extern "C" int mk_set_schedule(void *handle, const int32_t *instructions, int32_
         return fail(MK_ERR_RESIDENCY, "worker grid (%d) exceeds co-resident capacity (%d SMs x %d)", workers, h->sm_count, h->resident);
     if (workers > h->sm_count)
         return fail(MK_ERR_RESIDENCY, "worker grid (%d) exceeds the physical SM count (%d)", workers, h->sm_count);
+    // The queues are read once on the host.  Every operand the device uses as an
+    // index is checked here, so that a hand-built instruction tensor is refused
+    // before anything launches instead of writing outside the handle's buffers.
+    //
     // Down-projection folding mode (fold_down_blocks): spreading the folds over all
     // SMs needs every queue to hold a layer's down-projection instructions (opcode 6)
     // consecutively, which the reference's assignment policies all produce.  Any
     // other ordering gets the mode in which only the last slice's instruction folds.
     int owner_last = 0;
+    int first_layer = 0;
+    int local = 0;
     if (queue_len > 0) {
         const size_t words = (size_t)workers * queue_len * kInstrWords;
         int32_t *host = new (std::nothrow) int32_t[words];
         if (!host) return fail(MK_ERR_BAD_ARGUMENT, "mk_set_schedule: out of host memory");
         cudaError_t e = cudaMemcpy(host, instructions, words * sizeof(int32_t), cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) { delete[] host; return cuda_fail(e, "cudaMemcpy(instructions)"); }
+        const Params &p = h->params;
+        const int slots = p.max_partials < kTaggedPartials ? p.max_partials : kTaggedPartials;  // attention slices addressable
+        const int hidden_blocks = p.hidden / kBlockRows;
+        int lowest = p.layers;
+        for (int w = 0; w < workers; ++w) {
+            for (int q = 0; q < queue_len; ++q) {
+                const int32_t *ins = host + ((size_t)w * queue_len + q) * kInstrWords;
+                const int op = ins[0];
+                const char *why = nullptr;
+                auto blocks_ok = [](int b0, int b1, int limit) { return 0 <= b0 && b0 <= b1 && b1 <= limit; };
+                if (op == 0) continue;
+                if (op < 0 || op > 7) why = "opcode outside 0..7";
+                else if (op != 7 && (ins[1] < 0 || ins[1] >= p.layers)) why = "layer outside the model";
+                else if (op == 1 && !blocks_ok(ins[2], ins[3], p.qkv_rows / kBlockRows)) why = "QKV row blocks outside the matrix";
+                else if (op == 2 && (ins[2] < 0 || ins[2] >= p.hkv)) why = "KV head outside the model";
+                else if (op == 2 && (ins[3] < 1 || ins[3] > slots || ins[4] < 0 || ins[4] >= ins[3])) why = "attention slice outside 0..min(32, max_partials)";
+                else if (op == 3 && (ins[2] < 0 || ins[2] + kGroup > p.hq)) why = "query heads outside the model";
+                else if (op == 3 && (ins[5] < 1 || 6 + ins[5] + 1 > kInstrWords)) why = "reduction list does not fit the instruction";
+                else if ((op == 4 || op == 6) && !blocks_ok(ins[2], ins[3], hidden_blocks)) why = "output row blocks outside the matrix";
+                else if (op == 6 && (ins[4] < 0 || ins[4] >= p.down_slices)) why = "column slice outside the down projection";
+                else if (op == 5 && (ins[2] < 0 || 3 + ins[2] > kInstrWords)) why = "block list does not fit the instruction";
+                else if (op == 7 && !blocks_ok(ins[1], ins[2], p.vocab / kBlockRows)) why = "vocabulary row blocks outside the matrix";
+                if (!why && op == 3) {
+                    for (int j = 0; j < ins[5]; ++j)
+                        if (ins[6 + j] < 0 || ins[6 + j] >= slots) why = "reduction list entry outside 0..min(32, max_partials)";
+                    if (!ins[4] && (ins[6 + ins[5]] < 0 || ins[6 + ins[5]] >= slots)) why = "output slice outside 0..min(32, max_partials)";
+                }
+                if (!why && op == 5) {
+                    for (int j = 0; j < ins[2]; ++j)
+                        if (ins[3 + j] < 0 || ins[3 + j] >= p.inter / kBlockRows) why = "gate/up row block outside the matrix";
+                }
+                if (why) {
+                    delete[] host;
+                    return fail(MK_ERR_BAD_ARGUMENT, "mk_set_schedule: worker %d slot %d opcode %d: %s", w, q, op, why);
+                }
+                if (op != 7 && ins[1] < lowest) lowest = ins[1];
+            }
+        }
+        first_layer = lowest < p.layers ? lowest : 0;
+        // Local folding: every queue holds the column slices of its down-projection row
+        // blocks as consecutive instructions (no-ops aside) in slice order 0..S-1.
+        local = 1;
+        for (int w = 0; w < workers && local; ++w) {
+            int expect = 0, layer = -1, b0 = -1, b1 = -1;  // next slice expected within the current run
+            for (int q = 0; q < queue_len && local; ++q) {
+                const int32_t *ins = host + ((size_t)w * queue_len + q) * kInstrWords;
+                if (ins[0] != 6) { if (expect != 0) local = 0; continue; }  // a run has no gaps, not even no-ops
+                if (expect == 0) { layer = ins[1]; b0 = ins[2]; b1 = ins[3]; }
+                if (ins[1] != layer || ins[2] != b0 || ins[3] != b1 || ins[4] != expect || b1 - b0 > kLocalBlocks) local = 0;
+                expect = (expect + 1) % p.down_slices;
+            }
+            if (expect != 0) local = 0;
+        }
         for (int w = 0; w < workers && !owner_last; ++w) {
             int run_layer = -1;            // layer of the run of opcode-6 instructions being read, -1 outside a run
             unsigned long long seen = 0;   // layers whose run has ended (layers >= 64 fall back at once)
@@ -1943,6 +2098,9 @@ extern "C" int mk_set_schedule(void *handle, const int32_t *instructions, int32_
         }
         delete[] host;
     }
+    h->params.first_layer = first_layer;
+    h->fold_local_detected = local;
+    h->params.down_local = local && !h->fold_last_forced && !h->fold_spread_forced;
     h->fold_last_detected = owner_last;
     h->params.down_owner_last = owner_last || h->fold_last_forced;
     h->params.instructions = instructions;
@@ -1997,6 +2155,7 @@ extern "C" int mk_query(void *handle, MkLaunchInfo *info) {
     info->resident_ctas_per_sm = h->resident;
     info->queue_len = h->params.queue_len;
     info->scratch_bytes = (int64_t)h->scratch_bytes;
+    info->down_fold_mode = h->params.down_local ? 2 : (h->params.down_owner_last ? 1 : 0);
     return 0;
 }
 
@@ -2043,6 +2202,11 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     case MK_OPT_DOWN_FOLD_LAST:
         h->fold_last_forced = value != 0;
         h->params.down_owner_last = h->fold_last_detected || h->fold_last_forced;
+        h->params.down_local = h->fold_local_detected && !h->fold_last_forced && !h->fold_spread_forced;
+        return 0;
+    case MK_OPT_DOWN_FOLD_LOCAL:
+        h->fold_spread_forced = value == 0;
+        h->params.down_local = h->fold_local_detected && !h->fold_last_forced && !h->fold_spread_forced;
         return 0;
     case MK_OPT_EARLY_POLL_SHIFT:
         if (value < 0 || value > 31) return fail(MK_ERR_BAD_ARGUMENT, "early-poll shift must be 0..31");
@@ -2077,13 +2241,21 @@ extern "C" int mk_tp_init(void *handle, int32_t rank, int32_t world, int32_t voc
     return 0;
 }
 
-extern "C" int mk_tp_connect(void *handle, const void *ipc_handles) {
+extern "C" int mk_tp_connect(void *handle, const void *ipc_handles, int32_t count) {
     Handle *h = (Handle *)handle;
     if (!h || !ipc_handles) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_connect: null argument");
     if (!h->xchg || h->tp_world_pending < 2) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_connect: call mk_tp_init first");
     if (h->params.tp_world > 1) return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_connect: already connected");
+    if (count != h->tp_world_pending)
+        return fail(MK_ERR_BAD_ARGUMENT, "mk_tp_connect: %d handles given, mk_tp_init was told %d ranks", count, h->tp_world_pending);
     cudaError_t e = cudaSetDevice(h->device);
     if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    // Steps made on this handle before connecting (a single-GPU warm-up) left cells
+    // tagged 1, 2, ...; the launch count restarts at 1 below, so those cells are
+    // cleared: no launch after the restart may accept one of them as its own.
+    e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemset(h->scratch, 0, (size_t)((uint8_t *)h->params.argmax_key - (uint8_t *)h->scratch));
+    if (e != cudaSuccess) return cuda_fail(e, "clearing the hand-off cells");
     const cudaIpcMemHandle_t *handles = (const cudaIpcMemHandle_t *)ipc_handles;
     for (int r = 0; r < h->tp_world_pending; ++r) {
         if (r == h->params.tp_rank) {

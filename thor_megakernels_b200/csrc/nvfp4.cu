@@ -11,6 +11,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include "../../include/b200_megakernel.h"
 #include "mk_device.cuh"
@@ -159,7 +160,9 @@ static cudaError_t launch_gemv(const void *w, const void *packed, const void *sc
 
 // tensor-core path (gemv.cu); needs k to be a multiple of 256
 cudaError_t launch_gemv_mma(const void *w, const void *packed, const void *scales, const void *x, void *y, int m, int k,
-                            float ts, int is_packed, int batch, cudaStream_t stream);
+                            float ts, int is_packed, int batch, void *workspace, cudaStream_t stream);
+size_t gemv_workspace_bytes(int m, int k);
+void set_last_error(const char *msg);  // megakernel.cu: text for mk_last_error
 
 }  // namespace mk
 
@@ -175,13 +178,28 @@ extern "C" int mk_nvfp4_quantize(const void *input_bf16, void *packed, void *sca
     return (int)cudaGetLastError();
 }
 
+extern "C" int64_t mk_gemv_workspace_bytes(int32_t m, int32_t k) {
+    if (m <= 0 || k <= 0 || (k % 256) != 0) return 0;  // widths that are not a multiple of 256 run without scratch
+    return (int64_t)mk::gemv_workspace_bytes(m, k);
+}
+
 extern "C" int mk_gemv(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y, int32_t m,
-                       int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream) {
+                       int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *workspace,
+                       int64_t workspace_bytes, void *stream) {
     if (!x || !y || m <= 0 || k <= 0 || (k % 32) != 0 || batch < 1 || batch > 8) return cudaErrorInvalidValue;
     if (is_packed ? (!packed || !scales) : !w_bf16) return cudaErrorInvalidValue;
-    if (k % 256 == 0)
-        return (int)mk::launch_gemv_mma(w_bf16, packed, scales, x, y, m, k, tensor_scale, is_packed, batch,
+    if (k % 256 == 0) {
+        const int64_t need = (int64_t)mk::gemv_workspace_bytes(m, k);
+        if (need > 0 && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))) {
+            char msg[200];
+            snprintf(msg, sizeof(msg), "mk_gemv: m=%d k=%d needs a 256-byte aligned workspace of %lld bytes (mk_gemv_workspace_bytes), got %lld",
+                     m, k, (long long)need, (long long)(workspace ? workspace_bytes : 0));
+            mk::set_last_error(msg);
+            return MK_ERR_BAD_ARGUMENT;
+        }
+        return (int)mk::launch_gemv_mma(w_bf16, packed, scales, x, y, m, k, tensor_scale, is_packed, batch, workspace,
                                         (cudaStream_t)stream);
+    }
     // odd widths: plain warp-per-row kernel
     if (is_packed) {
         return (int)mk::launch_gemv<true>(nullptr, packed, scales, x, y, m, k, tensor_scale, batch, (cudaStream_t)stream);

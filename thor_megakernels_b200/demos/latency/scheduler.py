@@ -168,16 +168,37 @@ def schedule_downproj(globs: Globals, layer_idx: int):
     return out
 
 
+def schedule_downproj_rows_together(globs: Globals, layer_idx: int):
+    """Every worker gets a contiguous range of output row blocks and ALL column
+    slices of it, listed slice 0, 1, ... one after the other.  Same instruction
+    type and wire format as ``schedule_downproj``; with the ``rrk`` assignment a
+    worker then adds its slices to the residual stream by itself, in the
+    interpreter's slice order, instead of handing partial sums to another SM.
+    Not a reference layout (its down projection always splits rows AND columns
+    across workers, ``latency/scheduler.py:165-199``)."""
+    row_blocks = assert_div(globs.hidden_size, globs.down_proj_block_size)
+    col_slices = assert_div(globs.intermediate_size, globs.matvec_reduction_size)
+    out = []
+    for start, end in _even_ranges(row_blocks, globs.sm_count()):
+        if end > start:
+            out.extend(DownProjResidual(layer_idx, start, end, c) for c in range(col_slices))
+    return out
+
+
 def schedule_lm_head(globs: Globals):
     blocks = assert_div(globs.vocab_size, globs.lm_head_block_size)
     return [RMS_LM_Head(start, end) for start, end in _even_ranges(blocks, globs.sm_count())]
 
 
-def make_dag(globs: Globals, stop_after_op: str | None = None, layer_limit: int | None = None):
+def make_dag(globs: Globals, stop_after_op: str | None = None, layer_limit: int | None = None, first_layer: int = 0):
+    """``layer_limit`` and ``stop_after_op`` cut the schedule short as in the
+    reference; ``first_layer`` (not in the reference) starts it at a later layer,
+    whose input is then ``hidden_states`` as given: one layer can be run alone
+    from a recorded residual stream."""
     layers = globs.num_hidden_layers if layer_limit is None else layer_limit
     nodes: list[DAG_Node] = []
     frontier: list[DAG_Node] = []
-    for layer in range(layers):
+    for layer in range(first_layer, layers):
         added, frontier = make_dag_layer(globs, layer, frontier, stop_after_op)
         nodes.extend(added)
 
@@ -259,7 +280,8 @@ def make_dag_layer(globs: Globals, layer_idx: int, prev_layer_outputs: list[DAG_
     # -- down projection ---------------------------------------------------
     ordered = getattr(globs, "ordered_downproj", False)
     down_nodes: list[DAG_Node] = []
-    for ins in schedule_downproj(globs, layer_idx):
+    together = getattr(globs, "down_rows_together", False)
+    for ins in (schedule_downproj_rows_together if together else schedule_downproj)(globs, layer_idx):
         # An ordered bf16 reduction waits for the previous column slice.
         earlier = [n for n in down_nodes if ordered and n.instruction.reduction_block_idx == ins.reduction_block_idx - 1]
         down_nodes.append(DAG_Node(ins, upgate_nodes + earlier))
@@ -275,14 +297,32 @@ class LatencyScheduleBuilder(ScheduleBuilder):
         return make_globals(model, skip_attn_reduction, num_attention_partitions)
 
     @classmethod
-    def make_dag(cls, globs, stop_after_op: str | None = None, layer_limit: int | None = None):
-        return make_dag(globs, stop_after_op, layer_limit)
+    def make_dag(cls, globs, stop_after_op: str | None = None, layer_limit: int | None = None, first_layer: int = 0):
+        return make_dag(globs, stop_after_op, layer_limit, first_layer)
 
     @classmethod
     def build(cls, model, stop_after_op=None, layer_limit=None, skip_attn_reduction: bool = True,
-              num_attention_partitions: int = 1):
+              num_attention_partitions: int = 1, first_layer: int = 0, down_rows_together: bool = False):
+        """``down_rows_together``: lay the down projection out so that one worker
+        owns all column slices of its output rows (``schedule_downproj_rows_together``;
+        assign with policy ``rrk``).  The default is the reference's layout."""
         from ...scheduler import Schedule
 
         globs = cls.make_globals(model, skip_attn_reduction, num_attention_partitions)
-        nodes, end = cls.make_dag(globs, stop_after_op, layer_limit)
+        globs.down_rows_together = down_rows_together
+        nodes, end = cls.make_dag(globs, stop_after_op, layer_limit, first_layer)
         return Schedule(globs, nodes, end)
+
+
+def build_b200_schedule(model, **kwargs):
+    """The schedule this library runs fastest: the reference's instruction set
+    and per-op work splits, with the down projection laid out so that one SM owns
+    all column slices of its output rows (``down_rows_together``) and the
+    row-keeping round-robin assignment (``rrk``).  Returns a ``Schedule`` whose
+    ``globs.instructions`` / ``globs.timings`` are already filled.  Keyword
+    arguments go to ``LatencyScheduleBuilder.build``."""
+    from ...scheduler import assign_to_sms, tensorize_instructions
+
+    sched = LatencyScheduleBuilder.build(model, down_rows_together=True, **kwargs)
+    tensorize_instructions(sched.globs, assign_to_sms("rrk", schedule=sched))
+    return sched

@@ -56,10 +56,30 @@ def quantize_weight(weight: torch.Tensor, tensor_scale: float | None = None, ref
     return Nvfp4Weight(packed, scales, ts, rows, k, decoded)
 
 
-def gemv(weight: Nvfp4Weight | torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Split-K scratch for ``gemv`` calls that do not bring their own: one
+    buffer per (device, stream), grown on demand.  Calls on one stream run in
+    order, so they can share it; calls on different streams get different
+    buffers."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def gemv(weight: Nvfp4Weight | torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None,
+         workspace: torch.Tensor | None = None) -> torch.Tensor:
     """``y[b] = W @ x[b]`` for ``x`` of shape ``[k]`` or ``[batch <= 8, k]`` (bf16),
     fp32 accumulation, bf16 result.  ``weight`` is an ``Nvfp4Weight`` (fused
-    dequantisation) or a plain bf16 matrix."""
+    dequantisation) or a plain bf16 matrix.  ``workspace``: a uint8 CUDA tensor
+    of at least ``mk_gemv_workspace_bytes(rows, k)`` bytes for the split-K sums
+    (needed when k > 2048); by default a per-stream buffer owned by this module.
+    The library call itself never allocates."""
     if x.device.type != "cuda" or x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("x must be a contiguous bf16 CUDA tensor")
     squeeze = x.ndim == 1
@@ -72,17 +92,21 @@ def gemv(weight: Nvfp4Weight | torch.Tensor, x: torch.Tensor, out: torch.Tensor 
         raise ValueError(f"x has {k} columns, weight has {wk}")
     y = out if out is not None else torch.empty((batch, rows), dtype=torch.bfloat16, device=x.device)
     lib = _lib.load()
+    need = int(lib.mk_gemv_workspace_bytes(rows, k))
+    if need and workspace is None:
+        workspace = _workspace(x.device, need)
+    ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if need else (None, 0)
     with torch.cuda.device(x.device):
         if is_packed:
             code = lib.mk_gemv(None, weight.packed.data_ptr(), weight.scales.data_ptr(), xb.data_ptr(), y.data_ptr(),
-                               rows, k, weight.tensor_scale, 1, batch, _stream(x))
+                               rows, k, weight.tensor_scale, 1, batch, ws_ptr, ws_bytes, _stream(x))
         else:
             if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
                 raise ValueError("weight must be contiguous bf16")
             code = lib.mk_gemv(weight.data_ptr(), None, None, xb.data_ptr(), y.data_ptr(), rows, k, 1.0, 0, batch,
-                               _stream(x))
+                               ws_ptr, ws_bytes, _stream(x))
     if code != 0:
-        raise _lib.MegakernelError(code, f"mk_gemv refused m={rows} k={k} batch={batch}")
+        raise _lib.MegakernelError(code, lib.mk_last_error().decode() or f"mk_gemv refused m={rows} k={k} batch={batch}")
     return y.view(-1) if squeeze and out is None else y
 
 

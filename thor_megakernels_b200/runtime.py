@@ -223,7 +223,8 @@ class Megakernel:
             raise ValueError("every IPC handle must be 64 bytes")
         blob = C.create_string_buffer(b"".join(handles), len(handles) * _lib.MK_TP_HANDLE_BYTES)
         with torch.cuda.device(self.device):
-            _lib.check(self.lib.mk_tp_connect(self.handle, blob))
+            # the library checks the count against the world size given to tp_init
+            _lib.check(self.lib.mk_tp_connect(self.handle, blob, len(handles)))
 
     def set_wait_budget(self, cycles: int):
         _lib.check(self.lib.mk_set_wait_budget(self.handle, int(cycles)))

@@ -214,6 +214,30 @@ def round_robin_assign_to_sms(instructions, sm_count: int):
     return queues
 
 
+def row_keeping_assign_to_sms(instructions, sm_count: int):
+    """Round robin, except that instructions which reduce different column
+    slices into the SAME output rows of a layer (``reduction_block_idx`` differs,
+    layer and row blocks equal) all go to the worker that got the first of them.
+    With a builder that lists the slices of a row range one after the other
+    (``down_rows_together``), a worker then holds every slice of its rows in
+    slice order and can add them up itself.  Not a reference policy."""
+    _require_workers(sm_count)
+    queues = [[] for _ in range(sm_count)]
+    home: dict = {}
+    cursor = 0
+    for ins in instructions:
+        if hasattr(ins, "reduction_block_idx"):
+            key = (type(ins), ins.layer_idx, ins.start_block_idx, ins.end_block_idx)
+            if key not in home:
+                home[key] = cursor % sm_count
+                cursor += 1
+            queues[home[key]].append(ins)
+        else:
+            queues[cursor % sm_count].append(ins)
+            cursor += 1
+    return queues
+
+
 def zig_zag_assign_to_sms(instructions, sm_count: int):
     """Boustrophedon order: 0..n-1, n-1..0, 0..n-1, ..."""
     _require_workers(sm_count)
@@ -304,6 +328,8 @@ def assign_to_sms(
 
     if mode == "rr":
         queues = round_robin_assign_to_sms(instructions, sm_count)
+    elif mode == "rrk":
+        queues = row_keeping_assign_to_sms(instructions, sm_count)
     elif mode == "zz":
         queues = zig_zag_assign_to_sms(instructions, sm_count)
     elif mode == "wave":

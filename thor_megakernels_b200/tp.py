@@ -111,7 +111,7 @@ class TensorParallelDecoder:
     model can be dropped afterwards.  ``decode`` must be called by all ranks with
     the same arguments and returns the same tokens on every rank."""
 
-    def __init__(self, model, rank: int, world: int, schedule: str = "rr", group=None,
+    def __init__(self, model, rank: int, world: int, schedule: str = "b200", group=None,
                  num_attention_partitions: int = 1, nvfp4_weights: bool = False):
         import torch.distributed as dist
 
@@ -122,9 +122,11 @@ class TensorParallelDecoder:
         self.rank, self.world = rank, world
         self.local = shard_model(model, rank, world)
         split = num_attention_partitions > 1
+        together = schedule == "b200"  # one SM owns all column slices of its down-projection rows
         self.schedule = LatencyScheduleBuilder.build(self.local, skip_attn_reduction=not split,
-                                                     num_attention_partitions=num_attention_partitions)
-        tensorize_instructions(self.schedule.globs, assign_to_sms(schedule, schedule=self.schedule))
+                                                     num_attention_partitions=num_attention_partitions,
+                                                     down_rows_together=together)
+        tensorize_instructions(self.schedule.globs, assign_to_sms("rrk" if together else schedule, schedule=self.schedule))
         quantized = None
         if nvfp4_weights:  # every rank quantises its own shard (block scales run along K, which only o/down split)
             from .nvfp4 import quantize_model
