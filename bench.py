@@ -195,6 +195,13 @@ def make_schedule(model, schedule: str, **kwargs):
     return sched
 
 
+def apply_options(mk, args):
+    from thor_megakernels_b200 import _lib
+
+    if getattr(args, "l2_ahead", None) is not None:
+        mk.set_option(_lib.MK_OPT_L2_AHEAD_TILES, args.l2_ahead)
+
+
 def build_gpu_model(device, schedule: str = "b200"):
     from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
     from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
@@ -290,6 +297,7 @@ def run_ours(args, rank, world, local):
     model, sched = build_gpu_model(device, schedule=args.schedule)
     gen = MK_FusedGenerator(model, sched)
     mk = gen.mk
+    apply_options(mk, args)
     stream = torch.cuda.current_stream(device)
     first = torch.tensor([17], dtype=torch.int32, device=device)
     produced = torch.zeros(TOKENS_PER_REQUEST, dtype=torch.int32, device=device)
@@ -769,6 +777,31 @@ def run_headline_split(args, rank, world, local):
         print(json.dumps(line), flush=True)
 
 
+def build_step_model(args, device):
+    """Model + schedule of the timeline / profile-step workloads: the headline 1B
+    model (``--layers`` shrinks it), or with ``--arch 8b`` a few layers of the
+    Llama-3.1-8B shapes with ``--pos`` cached positions split into
+    ``--partitions`` attention slices per KV head."""
+    if args.arch == "8b":
+        from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+        from thor_megakernels_b200.model_types import ExtraModelConfig
+
+        cfg = dict(MODEL_8B, num_hidden_layers=args.layers or 4)
+        extra = ExtraModelConfig(interleave_rope=True, max_len_override=args.pos + 16)
+        model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=4, device=device, generate_on=device)
+        gen = torch.Generator(device=device).manual_seed(3)
+        for cache in model.stacked_kv_cache:
+            cache[:, :, :args.pos] = torch.randn(cache[:, :, :args.pos].shape, generator=gen, device=device).bfloat16()
+        sched = make_schedule(model, args.schedule, skip_attn_reduction=args.partitions == 1,
+                              num_attention_partitions=args.partitions)
+        sched.globs.barriers.zero_()
+        return model, sched, cfg
+    if args.layers is not None:
+        MODEL.update(num_hidden_layers=args.layers)
+    model, sched = build_gpu_model(device, schedule=args.schedule)
+    return model, sched, dict(MODEL)
+
+
 def run_timeline(args, rank, world, local):
     """One decode step with per-instruction clock stamps; prints, per opcode of a
     middle layer, when its instructions had their input, how long they streamed
@@ -782,7 +815,7 @@ def run_timeline(args, rank, world, local):
 
     device = torch.device(f"cuda:{local}")
     torch.cuda.set_device(device)
-    model, sched = build_gpu_model(device, schedule=args.schedule)
+    model, sched, cfg = build_step_model(args, device)
     g = sched.globs
     quantized = None
     if args.weights == "nvfp4":
@@ -790,6 +823,7 @@ def run_timeline(args, rank, world, local):
 
         quantized = quantize_model(model)
     mk = Megakernel.from_globals(g, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
+    apply_options(mk, args)
     tok = torch.tensor([17], dtype=torch.int32, device=device)
     out = torch.zeros(1, dtype=torch.int32, device=device)
     flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN
@@ -814,8 +848,8 @@ def run_timeline(args, rank, world, local):
     T = T / float(mhz)  # microseconds since the CTA started
     ops = I[:, :, 0]
     names = {1: "qkv", 2: "attention", 3: "attn_merge", 4: "o_proj", 5: "gate_up", 6: "down", 7: "lm_head"}
-    layers = MODEL["num_hidden_layers"]
-    mid = list(range(max(1, layers // 2 - 2), min(layers, layers // 2 + 2)))
+    layers = cfg["num_hidden_layers"]
+    mid = list(range(max(1, layers // 2 - 2), min(layers - 1, layers // 2 + 2))) or [layers - 1]
     rows, ends = [], {}
     for op in (1, 2, 3, 4, 5, 6):
         per_layer = []
@@ -842,10 +876,11 @@ def run_timeline(args, rank, world, local):
     m7 = ops == 7
     head = {"input_ready_us": [float(T[:, :, 49][m7].min()), float(T[:, :, 49][m7].max())],
             "last_use_us": [float(T[:, :, 52][m7].min()), float(T[:, :, 52][m7].max())]}
-    weights_mb = (linear_weight_bytes(MODEL) - 2 * MODEL["vocab_size"] * MODEL["hidden_size"]) / layers / 1e6
+    weights_mb = (linear_weight_bytes(cfg) - 2 * cfg["vocab_size"] * cfg["hidden_size"]) / layers / 1e6
     if args.weights == "nvfp4":
         weights_mb *= 0.5625 / 2
-    print(json.dumps({"workload": f"one step at position {args.pos}, {args.weights} weights, schedule {args.schedule}",
+    print(json.dumps({"workload": f"one step at position {args.pos}, {args.arch} shapes ({layers} layers), {args.weights} weights, "
+                                  f"schedule {args.schedule}",
                       "ms_plain": plain_ms, "ms_with_stamps": stamped_ms, "layers_averaged": mid,
                       "layer_period_us": round(layer_us, 2), "layer_weight_MB": round(weights_mb, 1),
                       "times": "microseconds after the layer's first QKV instruction had its input; [earliest SM, latest SM]",
@@ -863,32 +898,14 @@ def run_profile_step(args, rank, world, local):
 
     device = torch.device(f"cuda:{local}")
     torch.cuda.set_device(device)
-    if args.arch == "8b":
-        # Llama-3.1-8B layer shapes with a long cache (attention split into slices), few layers to keep a capture small
-        from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
-        from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
-        from thor_megakernels_b200.model_types import ExtraModelConfig
-        from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
-
-        cfg = dict(MODEL_8B, num_hidden_layers=args.layers or 4)
-        extra = ExtraModelConfig(interleave_rope=True, max_len_override=args.pos + 16)
-        model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=4, device=device, generate_on=device)
-        gen = torch.Generator(device=device).manual_seed(3)
-        for cache in model.stacked_kv_cache:
-            cache[:, :, :args.pos] = torch.randn(cache[:, :, :args.pos].shape, generator=gen, device=device).bfloat16()
-        sched = make_schedule(model, args.schedule, skip_attn_reduction=args.partitions == 1,
-                              num_attention_partitions=args.partitions)
-        sched.globs.barriers.zero_()
-    else:
-        if args.layers is not None:
-            MODEL.update(num_hidden_layers=args.layers)
-        model, sched = build_gpu_model(device, schedule=args.schedule)
+    model, sched, _ = build_step_model(args, device)
     quantized = None
     if args.weights == "nvfp4":
         from thor_megakernels_b200.nvfp4 import quantize_model
 
         quantized = quantize_model(model)
     mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
+    apply_options(mk, args)
     tok = torch.tensor([17], dtype=torch.int32, device=device)
     out = torch.zeros(1, dtype=torch.int32, device=device)
     flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN
@@ -925,6 +942,7 @@ def main():
     ap.add_argument("--schedule", default="b200", choices=["b200", "rr", "zz", "wave", "dag"],
                     help="b200: one SM owns all column slices of its down-projection rows; others: the reference's "
                          "layout under that assignment policy")
+    ap.add_argument("--l2-ahead", type=int, default=None, help="weight tiles each SM prefetches into L2 beyond its ring")
     ap.add_argument("--pos", type=int, default=60, help="timeline / profile-step: position of the step")
     ap.add_argument("--layers", type=int, default=None, help="profile-step: shrink the model to this many layers")
     ap.add_argument("--arch", default="1b", choices=["1b", "8b"], help="profile-step: layer shapes")

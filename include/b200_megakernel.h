@@ -220,6 +220,8 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
                                       * row blocks as consecutive instructions in slice order, the SM adds them to
                                       * the residual itself (same bf16 sequence as the interpreter, no cells parked
                                       * for another SM); 0: always fold across SMs */
+#define MK_OPT_L2_AHEAD_TILES     5  /* weight tiles beyond the shared-memory ring that each SM's loader asks L2 to
+                                      * fetch ahead of time (cp.async.bulk.prefetch.L2); 0 = off */
 #define MK_OPT_MAX_INFLIGHT_TILES 2  /* weight tiles (64 KiB bf16 / 18 KiB NVFP4) one loader keeps in flight */
 #define MK_OPT_EARLY_POLL_SHIFT   1  /* consumers stop watching a dependency counter and poll the data cells
                                       * themselves once it is within target >> shift of its target; 31 = never */
@@ -300,6 +302,58 @@ int mk_gemv(const void *w_bf16, const void *packed, const void *scales, const vo
  */
 int mk_gemv_static(const void *w_bf16, const void *packed, const void *scales, const void *x, void *y,
                    int32_t m, int32_t k, float tensor_scale, int32_t is_packed, int32_t batch, void *stream);
+
+/*
+ * Batched decode linear y[b, n] = sum_k x[b, k] * W[n, k] for 1..128 sequences
+ * on the tcgen05 tensor cores: weights are the MMA's A operand in 128-row slabs
+ * (TMA tiles with 128-byte swizzle), the activation panel is the B operand
+ * (N = batch padded to 16/32/64/128), fp32 accumulators in tensor memory,
+ * tcgen05.ld epilogue.  The reference's operator of this shape is the in-VM
+ * linear include/ops/nvfp4_linear.cuh:52-173 (TMA operands, tcgen05.mma,
+ * TMEM accumulators, :136-160 epilogue); this entry point takes bf16 operands.
+ *
+ * w [n, k] and x [batch, k] are bf16 row-major device tensors, k a multiple of
+ * 64.  splits == 1: y [batch, n] bf16 is written.  splits > 1 (k / 64 must be
+ * a multiple of splits): K is divided over `splits` CTAs per slab and fp32
+ * partial sums go to partials [splits, batch, n] for the caller's next kernel
+ * to add in split order; y is not touched.  mk_linear_batched_splits suggests
+ * a split count that gives every SM work.  error_word: a device int32 the
+ * caller zeroes; set to 1 if a bounded wait inside the kernel ran out.  The
+ * call allocates nothing.
+ */
+int32_t mk_linear_batched_splits(int32_t n, int32_t k, int32_t sm_count);
+int mk_linear_batched(const void *w_bf16, const void *x_bf16, void *y_bf16, float *partials,
+                      int32_t n, int32_t k, int32_t batch, int32_t splits, int32_t *error_word, void *stream);
+
+/*
+ * Batched decode: one step for 1..128 sequences, each at its own position.
+ * The operations are those of the reference's batched instruction set
+ * (megakernels/demos/throughput/instructions.py:57-223; interpreter
+ * throughput/python_vm.py:44-465), except that every sequence has its own
+ * position id (the reference uses one pos_id for the whole batch) and the
+ * rotary embedding is the adjacent-pair form of the batch-1 path, so one model
+ * container serves both.  Linears run on the tcgen05 tensor cores
+ * (mk_linear_batched); what lies between them are small stream-ordered kernels.
+ *
+ * mk_batched_create: `desc` as for mk_create with bf16 weights and embed_w;
+ *   k_cache / v_cache [L, kv_batch >= max_batch, kv_max_len, Hkv, D];
+ *   hidden_states [max_batch, hidden] and logits [max_batch, vocab] (bf16) are
+ *   the step's residual-stream and logits outputs.  The other activation
+ *   pointers, barriers and counters of `desc` are not used.  Allocates the
+ *   handle's workspace with one cudaMalloc.
+ * mk_step_batched: tokens_in / pos_ids / tokens_out are device int32 [batch];
+ *   sequence b reads cache rows 0..pos_ids[b]-1 of cache slot b, appends its new
+ *   row at pos_ids[b] and writes its greedy token (lowest index on ties).
+ *   tokens_out may be NULL.  Asynchronous on `stream`; allocates nothing, so it
+ *   can be captured in a CUDA graph.
+ * mk_batched_status: synchronises `stream`; MK_ERR_DEVICE_WAIT if a bounded
+ *   wait inside a linear ran out.
+ */
+int mk_batched_create(const MkModelDesc *desc, int32_t max_batch, void **handle);
+int mk_step_batched(void *handle, const int32_t *tokens_in, const int32_t *pos_ids, int32_t batch,
+                    int32_t *tokens_out, void *stream);
+int mk_batched_status(void *handle, void *stream);
+void mk_batched_destroy(void *handle);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,129 @@
+"""Batched-decode linear on the tcgen05 tensor cores against the oracle for a
+dense linear with bf16 operands: ``F.linear(x.float(), w.float()).bfloat16()``
+(fp32 accumulation, one rounding), through the C-ABI.  Tolerance: the stated
+band ``|a - ref| <= 3e-2 + 1e-2 |ref|`` and relative L2 <= 1e-3."""
+import pytest
+import torch
+
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def oracle_linear(w, x):
+    return torch.nn.functional.linear(x.float().cpu(), w.float().cpu()).bfloat16().float()
+
+
+@pytest.mark.parametrize("n,k", [(128, 64), (256, 512), (3072, 2048), (2048, 8192), (128256, 2048), (1000, 2048)])
+@pytest.mark.parametrize("batch", [1, 16, 64, 128, 37])
+def test_linear_matches_the_oracle(n, k, batch):
+    from thor_megakernels_b200 import batched
+
+    gen = torch.Generator(device="cuda").manual_seed(n + k + batch)
+    w = (torch.randn(n, k, device="cuda", generator=gen) * 0.02).bfloat16()
+    x = torch.randn(batch, k, device="cuda", generator=gen).bfloat16()
+    got = batched.linear(w, x)
+    batched.check_errors()
+    assert got.shape == (batch, n)
+    want = oracle_linear(w, x)
+    assert rel_l2(got.float().cpu(), want) <= 1e-3
+    assert_close("linear", got, want)
+
+
+@pytest.mark.parametrize("n,k,batch", [(2048, 2048, 64), (2048, 8192, 16), (4096, 14336, 128)])
+def test_split_k_partials_add_up(n, k, batch):
+    from thor_megakernels_b200 import batched
+
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    w = (torch.randn(n, k, device="cuda", generator=gen) * 0.02).bfloat16()
+    x = torch.randn(batch, k, device="cuda", generator=gen).bfloat16()
+    splits = batched.suggested_splits(n, k)
+    assert splits > 1 and (k // 64) % splits == 0
+    parts = batched.linear(w, x, splits=splits)
+    batched.check_errors()
+    assert parts.shape == (splits, batch, n)
+    got = parts.sum(dim=0).bfloat16()   # split order
+    want = oracle_linear(w, x)
+    assert rel_l2(got.float().cpu(), want) <= 1e-3
+    assert_close("split-K linear", got, want)
+
+
+def test_bad_shapes_are_refused():
+    from thor_megakernels_b200 import batched
+    from thor_megakernels_b200._lib import MegakernelError
+
+    w = torch.zeros(128, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(MegakernelError):
+        batched.linear(w, torch.zeros(4, 96, dtype=torch.bfloat16, device="cuda"))      # k not a multiple of 64
+    w = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(MegakernelError):
+        batched.linear(w, torch.zeros(129, 128, dtype=torch.bfloat16, device="cuda"))   # batch above 128
+    with pytest.raises(ValueError):
+        batched.linear(w, torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda"))
+
+
+CFG = dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+           intermediate_size=8192, vocab_size=4096)
+
+
+@pytest.mark.parametrize("batch", [16, 5])
+def test_two_layer_model_independent_cache_lengths(batch):
+    """A 2-layer model, `batch` sequences with different cache lengths, two
+    steps.  Oracle: every sequence decoded on its own through the CPU
+    interpreter of the batch-1 instruction set (oracle/pyvm.py) on the same
+    weights, cache rows and tokens.  The batched step sums the down projection
+    in one fp32 pass where the interpreter adds four bf16-rounded slices, so
+    hidden state and logits are compared with the stated band."""
+    from helpers import build_schedule
+    from oracle import pyvm
+    from thor_megakernels_b200.batched import BatchedDecoder
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+
+    max_len = 96
+    gpu = LlamaForCausalLM.random_init(LlamaConfig(**CFG), ExtraModelConfig(interleave_rope=True, max_len_override=max_len,
+                                                                            max_batch_size=batch), seed=7, device="cuda")
+    cpu = LlamaForCausalLM.random_init(LlamaConfig(**CFG), ExtraModelConfig(interleave_rope=True, max_len_override=max_len),
+                                       seed=7, device="cpu")
+    assert torch.equal(gpu.stacked_params.down_proj.cpu(), cpu.stacked_params.down_proj)
+    gen = torch.Generator().manual_seed(3)
+    lengths = torch.randint(3, 70, (batch,), generator=gen)
+    lengths[0], lengths[-1] = 1, 64   # a sequence with a single cached row, and a block-aligned one
+    kv = [torch.randn(gpu.stacked_kv_cache[i].shape, generator=gen).bfloat16() for i in range(2)]
+    for i in range(2):
+        for b in range(batch):
+            kv[i][:, b, int(lengths[b]):] *= 100.0   # garbage beyond every sequence's own length
+        gpu.stacked_kv_cache[i].copy_(kv[i].cuda())
+    dec = BatchedDecoder(gpu, batch)
+    cpu_sched = build_schedule(cpu)
+    instr = cpu_sched.get_linear_instructions()
+    tokens = torch.randint(0, CFG["vocab_size"], (batch,), generator=gen).int()
+    pos = lengths.int()
+    for step in range(2):
+        got = dec.step(tokens.cuda(), pos.cuda())
+        dec.status()
+        want = []
+        for b in range(batch):
+            for i in range(2):
+                cpu.stacked_kv_cache[i][:, 0] = gpu.stacked_kv_cache[i][:, b].cpu()
+                cpu.stacked_kv_cache[i][:, 0, int(pos[b])] = 0     # the oracle appends this row itself
+            nxt = pyvm.pyvm_step(cpu, cpu_sched, instr, tokens[b].view(1, 1).long(), int(pos[b]))
+            g = cpu_sched.globs
+            assert_close(f"hidden[{b}]", dec.hidden[b], g.hidden_states)
+            assert_close(f"k row[{b}]", gpu.stacked_kv_cache[0][:, b, int(pos[b])], cpu.stacked_kv_cache[0][:, 0, int(pos[b])])
+            assert_close(f"v row[{b}]", gpu.stacked_kv_cache[1][:, b, int(pos[b])], cpu.stacked_kv_cache[1][:, 0, int(pos[b])])
+            state_logits = cpu.lm_head.lm_head.weight.float() @ pyvm.rms_norm(g.hidden_states, cpu.lm_head.input_norm.weight, cpu.config.rms_norm_eps).float()
+            assert_close(f"logits[{b}]", dec.logits[b], state_logits.bfloat16())
+            assert int(got[b]) == int(dec.logits[b].float().argmax()), "argmax kernel differs from argmax of the logits it read"
+            if int(got[b]) != int(nxt):
+                top2 = torch.topk(state_logits, 2).values
+                assert float(top2[0] - top2[1]) <= 0.125
+            want.append(int(nxt))
+        tokens = torch.tensor(want, dtype=torch.int32)
+        pos = pos + 1
+    dec.close()

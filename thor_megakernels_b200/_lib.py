@@ -27,6 +27,7 @@ MK_OPT_EARLY_POLL_SHIFT = 1
 MK_OPT_MAX_INFLIGHT_TILES = 2
 MK_OPT_DOWN_FOLD_LAST = 3
 MK_OPT_DOWN_FOLD_LOCAL = 4
+MK_OPT_L2_AHEAD_TILES = 5
 
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1
@@ -35,6 +36,8 @@ EXPORTED_SYMBOLS = [
     "mk_last_error", "mk_create", "mk_set_schedule", "mk_step", "mk_query", "mk_status",
     "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
     "mk_gemv_static", "mk_tp_init", "mk_tp_connect", "mk_gemv_workspace_bytes",
+    "mk_linear_batched", "mk_linear_batched_splits",
+    "mk_batched_create", "mk_step_batched", "mk_batched_status", "mk_batched_destroy",
 ]
 
 
@@ -112,12 +115,19 @@ def load() -> C.CDLL:
     lib.mk_gemv.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp, C.c_int64, vp]
     lib.mk_gemv_static.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
     lib.mk_gemv_workspace_bytes.argtypes = [i32, i32]
+    lib.mk_linear_batched.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
+    lib.mk_linear_batched_splits.argtypes = [i32, i32, i32]
+    lib.mk_batched_create.argtypes = [C.POINTER(MkModelDesc), i32, C.POINTER(vp)]
+    lib.mk_step_batched.argtypes = [vp, vp, vp, i32, vp, vp]
+    lib.mk_batched_status.argtypes = [vp, vp]
+    lib.mk_batched_destroy.argtypes = [vp]
+    lib.mk_batched_destroy.restype = None
     lib.mk_tp_init.argtypes = [vp, i32, i32, i32, vp]
     lib.mk_tp_connect.argtypes = [vp, vp, i32]
     lib.mk_abi_sizeof.argtypes = [i32]
     lib.mk_set_option.argtypes = [vp, i32, C.c_int64]
     for name in EXPORTED_SYMBOLS:
-        if name not in ("mk_last_error", "mk_destroy", "mk_gemv_workspace_bytes"):
+        if name not in ("mk_last_error", "mk_destroy", "mk_gemv_workspace_bytes", "mk_batched_destroy"):
             getattr(lib, name).restype = C.c_int
     lib.mk_gemv_workspace_bytes.restype = C.c_int64
     return lib

@@ -1,0 +1,150 @@
+"""Batched-decode operators (16..128 sequences per step) on the tcgen05 tensor
+cores, through the C-ABI library.
+
+``linear`` is the dense contraction every linear layer becomes once a decode
+step carries a batch: ``y[b, n] = sum_k x[b, k] * W[n, k]``.  The reference's
+operator of this shape is ``include/ops/nvfp4_linear.cuh:52-173``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+_error_words: dict = {}
+
+
+def _error_word(device: torch.device) -> torch.Tensor:
+    word = _error_words.get(device.index)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _error_words[device.index] = word
+    return word
+
+
+def suggested_splits(n: int, k: int, device=None) -> int:
+    sms = torch.cuda.get_device_properties(device or torch.cuda.current_device()).multi_processor_count
+    return int(_lib.load().mk_linear_batched_splits(n, k, sms))
+
+
+def linear(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, splits: int = 1,
+           partials: torch.Tensor | None = None) -> torch.Tensor:
+    """``weight`` bf16 ``[n, k]``, ``x`` bf16 ``[batch <= 128, k]``; returns bf16
+    ``[batch, n]`` (fp32 accumulation, one rounding).  With ``splits > 1`` the K
+    dimension is divided over several CTAs per 128-row slab and the fp32 partial
+    sums ``[splits, batch, n]`` are returned instead, to be added in split order
+    by the caller."""
+    for name, t in (("weight", weight), ("x", x)):
+        if t.device.type != "cuda" or t.dtype != torch.bfloat16 or not t.is_contiguous() or t.ndim != 2:
+            raise ValueError(f"{name} must be a contiguous 2-D bf16 CUDA tensor")
+    n, k = weight.shape
+    batch = x.shape[0]
+    if x.shape[1] != k:
+        raise ValueError(f"x has {x.shape[1]} columns, weight has {k}")
+    lib = _lib.load()
+    err = _error_word(x.device)
+    if splits == 1:
+        y = out if out is not None else torch.empty((batch, n), dtype=torch.bfloat16, device=x.device)
+        part_ptr = None
+    else:
+        y = None
+        if partials is None:
+            partials = torch.empty((splits, batch, n), dtype=torch.float32, device=x.device)
+        part_ptr = partials.data_ptr()
+    with torch.cuda.device(x.device):
+        _lib.check(lib.mk_linear_batched(weight.data_ptr(), x.data_ptr(), None if y is None else y.data_ptr(), part_ptr,
+                                         n, k, batch, splits, err.data_ptr(), _stream(x)))
+    return y if splits == 1 else partials
+
+
+class BatchedDecoder:
+    """Greedy decode of up to 128 sequences per step, each with its own cache
+    length (``mk_batched_create`` / ``mk_step_batched``).
+
+    ``model`` is a finalised model container whose caches were set up with
+    ``ExtraModelConfig(max_batch_size >= max_batch)``; sequence ``b`` lives in
+    cache slot ``b``.  After ``step`` the residual stream is in ``hidden``
+    ``[batch, hidden]`` and the logits in ``logits`` ``[batch, vocab]``."""
+
+    def __init__(self, model, max_batch: int):
+        import ctypes as C
+        import math
+
+        cfg = model.config
+        dev = model.device
+        sp = model.stacked_params
+        k, v = model.stacked_kv_cache
+        if k.shape[1] < max_batch:
+            raise ValueError(f"the model's cache holds {k.shape[1]} sequences, max_batch is {max_batch}")
+        self.device = torch.device(dev)
+        self.max_batch = max_batch
+        self.hidden = torch.zeros((max_batch, cfg.hidden_size), dtype=torch.bfloat16, device=dev)
+        self.logits = torch.zeros((max_batch, cfg.vocab_size), dtype=torch.bfloat16, device=dev)
+        embed = model.model.embed_tokens.embed_tokens.weight.data
+        head = model.lm_head.lm_head.weight.data
+        self._keep = [sp, k, v, embed, head, model.model.rope_cos, model.model.rope_sin, model.lm_head.input_norm.weight]
+        d = _lib.MkModelDesc()
+        d.abi_version, d.weight_format = _lib.MK_ABI_VERSION, _lib.MK_WEIGHTS_BF16
+        d.hidden_size, d.num_layers = cfg.hidden_size, cfg.num_hidden_layers
+        d.num_q_heads, d.num_kv_heads, d.head_dim = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        d.intermediate_size, d.vocab_size = cfg.intermediate_size, cfg.vocab_size
+        d.attn_scale, d.rms_norm_eps = 1 / math.sqrt(cfg.head_dim), float(cfg.rms_norm_eps)
+        d.qkv_w, d.o_w, d.up_w = sp.qkv_proj.data_ptr(), sp.o_proj.data_ptr(), sp.up_proj.data_ptr()
+        d.gate_w, d.down_w, d.lm_head_w = sp.gate_proj.data_ptr(), sp.down_proj.data_ptr(), head.data_ptr()
+        d.attn_norm_w, d.mlp_norm_w = sp.attn_ln_weight.data_ptr(), sp.mlp_ln_weight.data_ptr()
+        d.lm_head_norm_w, d.embed_w = model.lm_head.input_norm.weight.data_ptr(), embed.data_ptr()
+        d.k_cache, d.v_cache, d.kv_batch, d.kv_max_len = k.data_ptr(), v.data_ptr(), k.shape[1], k.shape[2]
+        d.rope_cos, d.rope_sin = model.model.rope_cos.data_ptr(), model.model.rope_sin.data_ptr()
+        d.rope_positions = model.model.rope_cos.shape[0]
+        d.hidden_states, d.logits = self.hidden.data_ptr(), self.logits.data_ptr()
+        self.kv_max_len = k.shape[2]
+        self.lib = _lib.load()
+        self.handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_batched_create(C.byref(d), max_batch, C.byref(self.handle)))
+
+    def step(self, tokens: torch.Tensor, pos_ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``tokens`` and ``pos_ids``: int32 CUDA vectors of the same length
+        (``<= max_batch``).  Returns the greedy tokens (int32)."""
+        for name, t in (("tokens", tokens), ("pos_ids", pos_ids)):
+            if t.device.type != "cuda" or t.dtype != torch.int32 or t.ndim != 1 or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous int32 CUDA vector")
+        batch = tokens.numel()
+        if pos_ids.numel() != batch:
+            raise ValueError("tokens and pos_ids differ in length")
+        if out is None:
+            out = torch.empty(batch, dtype=torch.int32, device=tokens.device)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_step_batched(self.handle, tokens.data_ptr(), pos_ids.data_ptr(), batch, out.data_ptr(),
+                                                _stream(tokens)))
+        return out
+
+    def status(self):
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_batched_status(self.handle, torch.cuda.current_stream(self.device).cuda_stream))
+
+    def close(self):
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            self.lib.mk_batched_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def check_errors(device=None) -> None:
+    """Synchronises and raises if a bounded wait inside a batched kernel ran out."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    torch.cuda.synchronize(device)
+    word = _error_words.get(device.index)
+    if word is not None and int(word.item()) != 0:
+        word.zero_()
+        raise _lib.MegakernelError(_lib.MK_ERR_DEVICE_WAIT, "a bounded wait inside a batched-decode kernel ran out")

@@ -1,0 +1,314 @@
+// The memory-bound operators of a batched decode step (16..128 sequences, each
+// with its own cache length): embedding gather, residual add + RMSNorm,
+// rotary embedding + KV append, decode attention over per-sequence cache
+// lengths, SiLU-gate product, greedy argmax.  The dense contractions between
+// them run on the tensor cores (linear_batched.cu).
+//
+// Arithmetic and bf16 rounding points are those of the reference's interpreter
+// applied to every sequence on its own (megakernels/demos/latency/python_vm.py:
+// RMSNorm :50-56, rotary + append :196-248, attention :277-346, SiLU product
+// :146-165, residual add :59-80; the batched instruction set names the same
+// steps, megakernels/demos/throughput/instructions.py:57-223).
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "batched_ops.cuh"
+#include "mk_device.cuh"
+
+namespace mk {
+namespace bo {
+
+constexpr int kNormThreads = 256;
+
+// LinOut (batched_ops.cuh) is the result of a batched linear as its consumers
+// read it: bf16 y [batch, n], or the fp32 split-K partial sums [splits, batch, n],
+// which are added here in split order, scaled and rounded to bf16 once - the
+// value y would hold.
+__device__ __forceinline__ float lin_value(const LinOut &o, int b, int i) {
+    if (o.partials == nullptr) return __bfloat162float(o.y[(size_t)b * o.n + i]);
+    float total = 0.f;
+    for (int s = 0; s < o.splits; ++s) total += o.partials[((size_t)s * o.batch + b) * o.n + i];
+    return round_bf16(total * o.scale);
+}
+
+// hidden[b] = embed[token[b]]
+__global__ void embed_kernel(const bf16 *__restrict__ embed, const int *__restrict__ tokens, bf16 *__restrict__ hidden,
+                             int hidden_size) {
+    const int b = blockIdx.x;
+    const uint4 *src = reinterpret_cast<const uint4 *>(embed + (size_t)__ldg(tokens + b) * hidden_size);
+    uint4 *dst = reinterpret_cast<uint4 *>(hidden + (size_t)b * hidden_size);
+    for (int i = threadIdx.x; i < hidden_size / 8; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
+// One CTA per sequence.  If a linear result is given (`add`), first the
+// interpreter's residual add  hidden[b] = bf16(hidden[b] + bf16(linear[b])),
+// then normed[b] = w * bf16(hidden[b] * rstd) with fp32 statistics.  `normed`
+// may be null (residual update only).
+__global__ void __launch_bounds__(kNormThreads)
+residual_norm_kernel(bf16 *__restrict__ hidden, const LinOut lin, int add, const bf16 *__restrict__ weight,
+                     bf16 *__restrict__ normed, int hidden_size, float eps) {
+    extern __shared__ float row[];  // hidden_size floats
+    __shared__ float red[kNormThreads / 32];
+    const int b = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden_size; i += kNormThreads) {
+        float h = __bfloat162float(hidden[(size_t)b * hidden_size + i]);
+        if (add) {
+            h = round_bf16(h + lin_value(lin, b, i));
+            hidden[(size_t)b * hidden_size + i] = __float2bfloat16_rn(h);
+        }
+        row[i] = h;
+        ss = fmaf(h, h, ss);
+    }
+    if (normed == nullptr) return;
+#pragma unroll
+    for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kNormThreads / 32; ++w) total += red[w];
+    const float rstd = 1.0f / sqrtf(total / (float)hidden_size + eps);
+    for (int i = threadIdx.x; i < hidden_size; i += kNormThreads) {
+        const float w = __bfloat162float(weight[i]);
+        normed[(size_t)b * hidden_size + i] = __float2bfloat16_rn(w * round_bf16(row[i] * rstd));
+    }
+}
+
+// qkv [batch, (Hq + 2 Hkv) D] (bf16 linear output) -> q with rotary embedding,
+// K (rotary) and V rows appended to the cache at each sequence's own position.
+// Adjacent-pair ("interleaved") rotary tables: (x0, x1) -> (x0 c - x1 s, x1 c + x0 s)
+// in fp32 with separately rounded products, one bf16 rounding of the sum.
+__global__ void rope_append_kernel(const LinOut qkv, const int *__restrict__ pos_ids,
+                                   const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
+                                   bf16 *__restrict__ q_out, bf16 *__restrict__ k_cache, bf16 *__restrict__ v_cache,
+                                   int layer, int batch, int kv_len, int hq, int hkv, int hd) {
+    const int b = blockIdx.x;
+    const int pos = __ldg(pos_ids + b);
+    const int q_dim = hq * hd, kv_dim = hkv * hd, total = q_dim + 2 * kv_dim;
+    const size_t cache_row = (((size_t)layer * batch + b) * kv_len + pos) * kv_dim;
+    for (int pair = threadIdx.x; pair < total / 2; pair += blockDim.x) {
+        const int i = 2 * pair;
+        const float x0 = lin_value(qkv, b, i), x1 = lin_value(qkv, b, i + 1);
+        float y0 = x0, y1 = x1;
+        if (i < q_dim + kv_dim) {
+            const int d = i % hd;
+            const float c0 = __ldg(rope_cos + (size_t)pos * hd + d), s0 = __ldg(rope_sin + (size_t)pos * hd + d);
+            const float c1 = __ldg(rope_cos + (size_t)pos * hd + d + 1), s1 = __ldg(rope_sin + (size_t)pos * hd + d + 1);
+            y0 = round_bf16(__fadd_rn(__fmul_rn(x0, c0), __fmul_rn(-x1, s0)));
+            y1 = round_bf16(__fadd_rn(__fmul_rn(x1, c1), __fmul_rn(x0, s1)));
+        }
+        const __nv_bfloat162 out = __floats2bfloat162_rn(y0, y1);
+        if (i < q_dim) *reinterpret_cast<__nv_bfloat162 *>(q_out + (size_t)b * q_dim + i) = out;
+        else if (i < q_dim + kv_dim) *reinterpret_cast<__nv_bfloat162 *>(k_cache + cache_row + (i - q_dim)) = out;
+        else *reinterpret_cast<__nv_bfloat162 *>(v_cache + cache_row + (i - q_dim - kv_dim)) = out;
+    }
+}
+
+// Decode attention of one (sequence, KV head): the 4 query heads of the group
+// over cache rows 0..pos (the row appended by this step included).  fp32 scores,
+// softmax and weighted sum, one bf16 rounding at the store.  4 warps per CTA;
+// a warp takes rows w, w+4, ... in batches of 8 so that 16 independent 128-byte
+// loads are in flight per warp; lane (h = lane/8, sub = lane%8) owns query head
+// h and DPL = D/8 head dimensions.  Many CTAs are resident per SM, which is what
+// keeps HBM busy here.
+constexpr int kAttnWarps = 4;
+constexpr int kAttnDepth = 8;
+
+template <int DPL>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+attention_batched_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ k_cache, const bf16 *__restrict__ v_cache,
+                         const int *__restrict__ pos_ids, bf16 *__restrict__ out, int layer, int batch, int kv_len,
+                         int hq, int hkv, float attn_scale) {
+    constexpr int V = DPL / 8, D = DPL * 8;
+    __shared__ float part[kAttnWarps][4][D + 2];
+    const int kv_head = blockIdx.x, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = lane >> 3, sub = lane & 7, d0 = sub * DPL;
+    const int seq_len = __ldg(pos_ids + b) + 1;
+    const size_t tok_stride = (size_t)hkv * D;
+    const size_t base = (((size_t)layer * batch + b) * kv_len) * tok_stride + (size_t)kv_head * D + d0;
+    const bf16 *kbase = k_cache + base, *vbase = v_cache + base;
+
+    float qf[DPL];
+    {
+        const bf16 *qp = q + (size_t)b * hq * D + (size_t)(kv_head * 4 + h) * D + d0;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            float tmp[8];
+            unpack8(*reinterpret_cast<const uint4 *>(qp + 8 * v), tmp);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qf[8 * v + i] = tmp[i];
+        }
+    }
+    float m = -INFINITY, l = 0.f, acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    const float scale_log2e = attn_scale * 1.4426950408889634f;
+
+    for (int t0 = warp; t0 < seq_len; t0 += kAttnWarps * kAttnDepth) {
+        uint4 kq[kAttnDepth][V], vq[kAttnDepth][V];
+#pragma unroll
+        for (int j = 0; j < kAttnDepth; ++j) {
+            const int t = t0 + j * kAttnWarps;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                kq[j][v] = vq[j][v] = make_uint4(0u, 0u, 0u, 0u);
+                if (t < seq_len) {
+                    kq[j][v] = __ldg(reinterpret_cast<const uint4 *>(kbase + (size_t)t * tok_stride) + v);
+                    vq[j][v] = __ldg(reinterpret_cast<const uint4 *>(vbase + (size_t)t * tok_stride) + v);
+                }
+            }
+        }
+        float sc[kAttnDepth];
+#pragma unroll
+        for (int j = 0; j < kAttnDepth; ++j) {
+            float d = 0.f;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                float kf[8];
+                unpack8(kq[j][v], kf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d = fmaf(qf[8 * v + i], kf[i], d);
+            }
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            sc[j] = (t0 + j * kAttnWarps < seq_len) ? d * scale_log2e : -INFINITY;
+        }
+        float mn = m;
+#pragma unroll
+        for (int j = 0; j < kAttnDepth; ++j) mn = fmaxf(mn, sc[j]);
+        const float corr = exp2f(m - mn);  // first batch: exp2(-inf) = 0; row t0 is always valid, so mn is finite
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+#pragma unroll
+        for (int j = 0; j < kAttnDepth; ++j) {
+            const float pr = exp2f(sc[j] - mn);
+            l += pr;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                float vf[8];
+                unpack8(vq[j][v], vf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[8 * v + i] = fmaf(pr, vf[i], acc[8 * v + i]);
+            }
+        }
+        m = mn;
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) part[warp][h][d0 + i] = acc[i];
+    if (sub == 0) {
+        part[warp][h][D] = m;
+        part[warp][h][D + 1] = l;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 4 * D; idx += kAttnWarps * 32) {
+        const int hh = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, part[w][hh][D]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float mw = part[w][hh][D];
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+            L = fmaf(part[w][hh][D + 1], f, L);
+            O = fmaf(part[w][hh][d], f, O);
+        }
+        out[(size_t)b * hq * D + (size_t)(kv_head * 4 + hh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+
+// act[b, i] = bf16(bf16(silu(gate[b, i])) * up[b, i]) from the two linears'
+// results.  With `round_silu` 0 the product is rounded once (the rule of the
+// reference's quantised model, tools/analysis/nvfp4/model_reference.py:39-61).
+__global__ void silu_mul_kernel(const LinOut up, const LinOut gate, bf16 *__restrict__ act, int batch, int inter, int round_silu) {
+    const size_t total = (size_t)batch * inter;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int b = (int)(idx / inter), i = (int)(idx % inter);
+        const float u = lin_value(up, b, i), g = lin_value(gate, b, i);
+        float a = g / (1.0f + expf(-g));
+        if (round_silu) a = round_bf16(a);
+        act[idx] = __float2bfloat16_rn(a * u);
+    }
+}
+
+// token[b] = argmax_i logits[b, i], lowest index on ties.  One CTA per sequence.
+__global__ void __launch_bounds__(256) argmax_kernel(const bf16 *__restrict__ logits, int *__restrict__ tokens, int vocab) {
+    __shared__ unsigned long long best_s[8];
+    const int b = blockIdx.x;
+    unsigned long long best = 0ull;
+    for (int i = threadIdx.x; i < vocab; i += 256) {
+        uint32_t bits = (uint32_t)__bfloat16_as_ushort(logits[(size_t)b * vocab + i]);
+        bits = (bits & 0x8000u) ? (~bits & 0xffffu) : (bits | 0x8000u);  // order-preserving
+        const unsigned long long key = ((unsigned long long)bits << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i);
+        if (key > best) best = key;
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+        const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, off);
+        if (o > best) best = o;
+    }
+    if ((threadIdx.x & 31) == 0) best_s[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (best_s[w] > best) best = best_s[w];
+        tokens[b] = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+    }
+}
+
+}  // namespace bo
+
+// launchers used by the batched step (batched_step.cu); declared in batched_ops.cuh
+cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int batch, int hidden_size, cudaStream_t st) {
+    bo::embed_kernel<<<batch, 128, 0, st>>>(embed, tokens, hidden, hidden_size);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_residual_norm(bf16 *hidden, const bo::LinOut &lin, int add, const bf16 *weight, bf16 *normed, int batch,
+                                 int hidden_size, float eps, cudaStream_t st) {
+    bo::residual_norm_kernel<<<batch, bo::kNormThreads, hidden_size * sizeof(float), st>>>(hidden, lin, add, weight, normed,
+                                                                                             hidden_size, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope_append(const bo::LinOut &qkv, const int *pos_ids, const float *rope_cos, const float *rope_sin, bf16 *q_out,
+                               bf16 *k_cache, bf16 *v_cache, int layer, int batch, int kv_len, int hq, int hkv, int hd,
+                               cudaStream_t st) {
+    bo::rope_append_kernel<<<batch, 256, 0, st>>>(qkv, pos_ids, rope_cos, rope_sin, q_out, k_cache, v_cache, layer, batch,
+                                                   kv_len, hq, hkv, hd);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attention_batched(const bf16 *q, const bf16 *k_cache, const bf16 *v_cache, const int *pos_ids, bf16 *out,
+                                     int layer, int batch, int kv_len, int hq, int hkv, int hd, float attn_scale,
+                                     cudaStream_t st) {
+    const dim3 grid(hkv, batch), block(bo::kAttnWarps * 32);
+    if (hd == 64)
+        bo::attention_batched_kernel<8><<<grid, block, 0, st>>>(q, k_cache, v_cache, pos_ids, out, layer, batch, kv_len, hq, hkv, attn_scale);
+    else
+        bo::attention_batched_kernel<16><<<grid, block, 0, st>>>(q, k_cache, v_cache, pos_ids, out, layer, batch, kv_len, hq, hkv, attn_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(const bo::LinOut &up, const bo::LinOut &gate, bf16 *act, int batch, int inter, int round_silu,
+                            cudaStream_t st) {
+    const size_t total = (size_t)batch * inter;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+    bo::silu_mul_kernel<<<blocks, 256, 0, st>>>(up, gate, act, batch, inter, round_silu);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax(const bf16 *logits, int *tokens, int batch, int vocab, cudaStream_t st) {
+    bo::argmax_kernel<<<batch, 256, 0, st>>>(logits, tokens, vocab);
+    return cudaGetLastError();
+}
+
+}  // namespace mk

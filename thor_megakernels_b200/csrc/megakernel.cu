@@ -103,6 +103,7 @@ struct Params {
     float attn_scale, eps;
     long long spin_cycles;
     int max_inflight;  // weight tiles a loader keeps in flight
+    int l2_ahead;      // weight tiles beyond the ring that a loader asks L2 to fetch ahead of time (0: none)
     int early_shift;  // consumers start polling cells once a counter is within expected >> early_shift of its target (31: never early)
     int o_cols, o_chunks, o_width;  // output projection: input columns (Hq*D), tiles per row block, columns per tile
     int down_width;   // columns of one down-projection slice (multiple of 256, at most 2048)
@@ -369,10 +370,12 @@ __device__ __forceinline__ const int *instruction_at(const Params &p, int slot) 
     return p.instructions + ((size_t)blockIdx.x * p.queue_len + slot) * kInstrWords;
 }
 
-// Pulls the next instruction's 128-byte line towards this SM while the current
-// instruction runs, so that reading its opcode later does not cost a trip to L2.
-__device__ __forceinline__ void prefetch_instruction(const Params &p, int slot) {
-    if (slot < p.queue_len) asm volatile("prefetch.global.L1 [%0];" ::"l"(instruction_at(p, slot)));
+// Opcode of the instruction in `slot` (0 beyond the queue).  Every role reads the
+// NEXT instruction's opcode while it still works on the current one: the load
+// brings the instruction's 128-byte line into this SM's L1, so that by the time
+// the role gets there neither the opcode nor the operand words cost a trip to L2.
+__device__ __forceinline__ int opcode_at(const Params &p, int slot) {
+    return slot < p.queue_len ? __ldg(instruction_at(p, slot)) : 0;
 }
 
 __device__ __forceinline__ void stamp(const Params &p, int slot, int event, long long t_start) {
@@ -411,6 +414,7 @@ template <int NCH, bool FP4>
 struct TileCursor {
     int slot = -1;
     int op = 0;
+    int next_op = -1;       // opcode of slot + 1, loaded while the tiles of `slot` are being issued (-1: not loaded yet)
     int idx = 0, cnt = 0;   // block position within the instruction
     int sub = 0, nsub = 1;  // tile position within the block
     int first_block = 0;
@@ -459,7 +463,8 @@ struct TileCursor {
             }
             if (++slot >= p.queue_len) return false;
             ins = instruction_at(p, slot);
-            op = __ldg(ins);
+            op = next_op >= 0 ? next_op : __ldg(ins);
+            next_op = opcode_at(p, slot + 1);
             idx = 0; sub = 0; cnt = 0; nsub = NCH; col0 = 0; width = kChunkCols;
             const size_t hidden = p.hidden;
             switch (op) {
@@ -518,7 +523,31 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
     TileCursor<NCH, FP4> tiles;
     Tile t;
     int last_slot = -1;
+    // Second cursor over the same queue, running up to l2_ahead tiles ahead of the
+    // fills: while the ring is full (its tiles wait for activations that are still
+    // being produced), HBM would otherwise sit idle; asking L2 for the tiles after
+    // the ring keeps it busy, and their later fills are served from L2.
+    TileCursor<NCH, FP4> ahead;
+    Tile ta;
+    int filled = 0, hinted = 0;
+    bool more_ahead = p.l2_ahead > 0;
     while (tiles.next(p, t)) {
+        while (more_ahead && hinted < filled + Fmt<FP4>::stages + p.l2_ahead) {
+            more_ahead = ahead.next(p, ta);
+            if (!more_ahead) break;
+            if (++hinted <= filled + Fmt<FP4>::stages) continue;  // the ring itself covers these
+            if constexpr (FP4) {
+                for (int r = 0; r < kBlockRows; ++r) {
+                    bulk_prefetch_l2(ta.src + r * ta.stride_bytes, ta.width / 2);
+                    bulk_prefetch_l2(ta.scales + r * ta.scale_stride, ta.width / 16);
+                }
+            } else if (ta.stride_bytes == (size_t)ta.width * 2) {
+                bulk_prefetch_l2(ta.src, kBlockRows * ta.width * 2);  // rows are contiguous: one request
+            } else {
+                for (int r = 0; r < kBlockRows; ++r) bulk_prefetch_l2(ta.src + r * ta.stride_bytes, ta.width * 2);
+            }
+        }
+        ++filled;
         if (t.slot != last_slot) {
             if (last_slot >= 0) stamp(p, last_slot, kEvLastLoad, t_start);
             stamp(p, t.slot, kEvLoaderStart, t_start);
@@ -1094,11 +1123,12 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
     const bf16 *step_input = p.hidden_states;
     if (p.flags & MK_STEP_EMBED) step_input = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
 
+    int next_op = opcode_at(p, 0);
 #pragma unroll 1
     for (int slot = 0; slot < p.queue_len; ++slot) {
         const int *ins = instruction_at(p, slot);
-        const int op = __ldg(ins);
-        if (lane == 0) prefetch_instruction(p, slot + 1);
+        const int op = next_op;
+        next_op = opcode_at(p, slot + 1);  // in flight while this instruction runs
         if (op == 0) continue;
         if (ctid == 0) stamp(p, slot, kEvConsumerStart, t_start);
         uint4 x[NCH][8];
@@ -1162,30 +1192,36 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
                 const int t = lane & 3;
                 const bool has_cols = ctid * 8 < width;  // narrower slices leave the upper threads without columns
                 const unsigned long long *silu = p.t_silu + ((size_t)layer * p.inter) / 2 + (ctid * 8) / 2;
-                uint4 mine = make_uint4(0u, 0u, 0u, 0u), nxt = make_uint4(0u, 0u, 0u, 0u);
+                // One round of loads fetches this thread's 8 values of EVERY slice; slices
+                // whose producers are not done yet are fetched again when their turn comes.
+                uint4 mine[kMaxDownSlices];
+                uint32_t valid = 0;
                 if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
+#pragma unroll
+                for (int r = 0; r < kMaxDownSlices; ++r) {
+                    mine[r] = make_uint4(0u, 0u, 0u, 0u);
+                    if (r < S && has_cols && try_load8(silu + ((size_t)r * width) / 2, tag, mine[r])) valid |= 1u << r;
+                }
                 named_barrier_sync(kConsumerBarrier, kConsumerThreads);  // everybody is done with the previous operand in xbuf
-                if (has_cols) load8_wait(p, s, silu, tag, mine, op, slot);
-                if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
-                for (int r = 0; r < S; ++r) {
+#pragma unroll
+                for (int r = 0; r < kMaxDownSlices; ++r) {
+                    if (r >= S) break;
                     if (ctid == 0 && r > 0) stamp(p, slot + r, kEvConsumerStart, t_start);
+                    if (has_cols && !(valid & (1u << r))) load8_wait(p, s, silu + ((size_t)r * width) / 2, tag, mine[r], op, slot + r);
+                    if (ctid == 0 && r == 0) stamp(p, slot, kEvDoneWait, t_start);
                     bf16 *half = s.xbuf + (r & 1) * kChunkCols;
-                    *reinterpret_cast<uint4 *>(&half[ctid * 8]) = mine;
+                    *reinterpret_cast<uint4 *>(&half[ctid * 8]) = mine[r];
+                    // the half written two slices ago is free: every thread passed the barrier of the slice in between
                     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
                     uint4 xs[1][8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) xs[0][j] = operand_convert<FP4>(lds128(&half[operand_column<FP4>(cw, t, j)]));
-                    bool ok = true;
-                    if (r + 1 < S && has_cols) ok = try_load8(silu + ((size_t)(r + 1) * width) / 2, tag, nxt);
                     if (ctid == 0) stamp(p, slot + r, kEvFirstUse, t_start);
                     for (int b = b0; b < b1; ++b) consume_block<1, FP4>(p, s, st, lane, cw, xs, op, slot + r, 1, width);
                     if (ctid == 0) stamp(p, slot + r, kEvLastUse, t_start);
-                    if (r + 1 < S) {
-                        if (!ok) load8_wait(p, s, silu + ((size_t)(r + 1) * width) / 2, tag, nxt, op, slot + r + 1);
-                        mine = nxt;
-                    }
                 }
                 slot += S - 1;  // the slices' instructions have been consumed
+                next_op = opcode_at(p, slot + 1);
                 continue;
             }
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
@@ -1429,11 +1465,12 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
     const bool pair_writer = writer && (lane & 1) == 0;  // ... and write the cell of rows (lane, lane+1)
     int run_start = -1, run_layer = -1;                 // consecutive down-projection instructions of one layer
 
+    int next_op = opcode_at(p, 0);
 #pragma unroll 1
     for (int slot = 0; slot < p.queue_len; ++slot) {
         const int *ins = instruction_at(p, slot);
-        const int op = __ldg(ins);
-        if (lane == 0) prefetch_instruction(p, slot + 1);
+        const int op = next_op;
+        next_op = opcode_at(p, slot + 1);  // in flight while this instruction runs
         if (op == 0) continue;
         if (lane == 0) stamp(p, slot, kEvStorerStart, t_start);
         switch (op) {
@@ -1572,42 +1609,58 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                 // `hidden += bf16(slice sum)` (python_vm.py:59-80) runs right here: no cells
                 // parked for another SM, no second hand-off.  The running value of a row
                 // stays in shared memory between the slices' instructions.
-                const bool last = red == p.down_slices - 1;
+                // The run's S instructions are handled here in one go (the queue position
+                // moves past them below): one look at the instruction words, the residual
+                // fetched once, one counter update.
+                const int S = p.down_slices;
                 const bool sum_fp32 = p.model_numerics || p.tp_world > 1;  // slices added in fp32, rounded once at the end
-                for (int b = b0; b < b1; ++b) {
-                    float h = 0.f;
-                    if (red == 0 && writer && !sum_fp32) {
-                        // residual entering the MLP block: written by the output projection long ago
-                        const int row = b * kBlockRows + lane;
+                const int nb = b1 - b0;
+                // residual entering the MLP block (written by the output projection long ago)
+                for (int i = 0; i < nb; ++i) {
+                    if (writer && p.tp_world == 1) {
+                        const int row = (b0 + i) * kBlockRows + lane;
                         const uint32_t pr = load1_wait(p, s, p.t_resid + ((size_t)layer * p.hidden + row) / 2, tag, op, slot);
-                        h = (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
+                        s.down_acc[i][lane] = (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
                     }
-                    const float y = collect_block(p, s, st, lane, op, slot);
-                    if (writer) {
-                        if (red != 0) h = s.down_acc[b - b0][lane];
-                        h = sum_fp32 ? h + y : round_bf16(h + round_bf16(y));
-                        s.down_acc[b - b0][lane] = h;
+                }
+                float total[kLocalBlocks];
+#pragma unroll
+                for (int i = 0; i < kLocalBlocks; ++i) total[i] = 0.f;
+                for (int r = 0; r < S; ++r) {
+                    if (lane == 0 && r > 0) stamp(p, slot + r, kEvStorerStart, t_start);
+#pragma unroll
+                    for (int i = 0; i < kLocalBlocks; ++i) {
+                        if (i >= nb) break;
+                        const float y = collect_block(p, s, st, lane, op, slot + r);
+                        if (writer) {
+                            if (sum_fp32) total[i] += y;
+                            else s.down_acc[i][lane] = round_bf16(s.down_acc[i][lane] + round_bf16(y));
+                        }
                     }
-                    if (!last) continue;
+                    if (lane == 0 && r + 1 < S) stamp(p, slot + r, kEvLastStore, t_start);
+                }
+#pragma unroll
+                for (int i = 0; i < kLocalBlocks; ++i) {
+                    if (i >= nb) break;
+                    const int b = b0 + i;
                     if (p.tp_world > 1) {
-                        if (writer && !aborted(s)) tp_push(p, tag, 1, layer, b * kBlockRows + lane, h * down_scale(p, layer));
+                        if (writer && !aborted(s)) tp_push(p, tag, 1, layer, b * kBlockRows + lane, total[i] * down_scale(p, layer));
                         continue;
                     }
-                    if (sum_fp32 && writer) {
-                        const int row = b * kBlockRows + lane;
-                        const uint32_t pr = load1_wait(p, s, p.t_resid + ((size_t)layer * p.hidden + row) / 2, tag, op, slot);
-                        const float r = (row & 1) ? bf16_hi(pr) : bf16_lo(pr);
-                        h = round_bf16(r + round_bf16(h * down_scale(p, layer)));
-                    }
+                    float h = writer ? s.down_acc[i][lane] : 0.f;
+                    if (sum_fp32) h = round_bf16(h + round_bf16(total[i] * down_scale(p, layer)));
                     const float h_next = __shfl_xor_sync(0xffffffffu, h, 1);
                     if (pair_writer && !aborted(s))
                         st_tagged(p.t_hidden + ((size_t)layer * p.hidden + b * kBlockRows + lane) / 2, pack_bf16x2(h, h_next), tag);
                 }
-                if (last && p.tp_world > 1)
+                if (p.tp_world > 1)
                     tp_fold_blocks(p, s, lane, tag, 1, layer, b0, b1, 1, nullptr, p.t_resid + (size_t)layer * (p.hidden / 2),
                                    p.t_hidden + (size_t)layer * (p.hidden / 2), op, slot);
-                publish(p, s, lane, counter(p, layer, 5, 0), b1 - b0);
-                break;
+                publish(p, s, lane, counter(p, layer, 5, 0), S * nb);  // what the S instructions add together
+                slot += S - 1;
+                next_op = opcode_at(p, slot + 1);
+                if (lane == 0) stamp(p, slot, kEvLastStore, t_start);
+                continue;
             }
             unsigned long long *mine = p.t_down + ((size_t)layer * p.down_slices + red) * p.hidden;
             for (int b = b0; b < b1; ++b) {
@@ -1951,6 +2004,7 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.spin_cycles = 4000000000ll;
     p.early_shift = 0;
     p.max_inflight = kMaxStages;
+    p.l2_ahead = 0;
     p.o_cols = o_cols;
     p.o_chunks = o_cols >= kChunkCols ? o_cols / kChunkCols : 1;
     p.o_width = o_cols >= kChunkCols ? kChunkCols : o_cols;
@@ -2207,6 +2261,10 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     case MK_OPT_DOWN_FOLD_LOCAL:
         h->fold_spread_forced = value == 0;
         h->params.down_local = h->fold_local_detected && !h->fold_last_forced && !h->fold_spread_forced;
+        return 0;
+    case MK_OPT_L2_AHEAD_TILES:
+        if (value < 0 || value > 64) return fail(MK_ERR_BAD_ARGUMENT, "L2 look-ahead must be 0..64 tiles");
+        h->params.l2_ahead = (int)value;
         return 0;
     case MK_OPT_EARLY_POLL_SHIFT:
         if (value < 0 || value > 31) return fail(MK_ERR_BAD_ARGUMENT, "early-poll shift must be 0..31");
