@@ -195,13 +195,6 @@ def make_schedule(model, schedule: str, **kwargs):
     return sched
 
 
-def apply_options(mk, args):
-    from thor_megakernels_b200 import _lib
-
-    if getattr(args, "l2_ahead", None) is not None:
-        mk.set_option(_lib.MK_OPT_L2_AHEAD_TILES, args.l2_ahead)
-
-
 def build_gpu_model(device, schedule: str = "b200"):
     from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder
     from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
@@ -297,7 +290,6 @@ def run_ours(args, rank, world, local):
     model, sched = build_gpu_model(device, schedule=args.schedule)
     gen = MK_FusedGenerator(model, sched)
     mk = gen.mk
-    apply_options(mk, args)
     stream = torch.cuda.current_stream(device)
     first = torch.tensor([17], dtype=torch.int32, device=device)
     produced = torch.zeros(TOKENS_PER_REQUEST, dtype=torch.int32, device=device)
@@ -823,7 +815,6 @@ def run_timeline(args, rank, world, local):
 
         quantized = quantize_model(model)
     mk = Megakernel.from_globals(g, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
-    apply_options(mk, args)
     tok = torch.tensor([17], dtype=torch.int32, device=device)
     out = torch.zeros(1, dtype=torch.int32, device=device)
     flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN
@@ -905,7 +896,6 @@ def run_profile_step(args, rank, world, local):
 
         quantized = quantize_model(model)
     mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
-    apply_options(mk, args)
     tok = torch.tensor([17], dtype=torch.int32, device=device)
     out = torch.zeros(1, dtype=torch.int32, device=device)
     flags = MK_STEP_EMBED | MK_STEP_RESET_BARRIERS | MK_STEP_WRITE_TOKEN
@@ -942,7 +932,6 @@ def main():
     ap.add_argument("--schedule", default="b200", choices=["b200", "rr", "zz", "wave", "dag"],
                     help="b200: one SM owns all column slices of its down-projection rows; others: the reference's "
                          "layout under that assignment policy")
-    ap.add_argument("--l2-ahead", type=int, default=None, help="weight tiles each SM prefetches into L2 beyond its ring")
     ap.add_argument("--pos", type=int, default=60, help="timeline / profile-step: position of the step")
     ap.add_argument("--layers", type=int, default=None, help="profile-step: shrink the model to this many layers")
     ap.add_argument("--arch", default="1b", choices=["1b", "8b"], help="profile-step: layer shapes")

@@ -220,8 +220,6 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
                                       * row blocks as consecutive instructions in slice order, the SM adds them to
                                       * the residual itself (same bf16 sequence as the interpreter, no cells parked
                                       * for another SM); 0: always fold across SMs */
-#define MK_OPT_L2_AHEAD_TILES     5  /* weight tiles beyond the shared-memory ring that each SM's loader asks L2 to
-                                      * fetch ahead of time (cp.async.bulk.prefetch.L2); 0 = off */
 #define MK_OPT_MAX_INFLIGHT_TILES 2  /* weight tiles (64 KiB bf16 / 18 KiB NVFP4) one loader keeps in flight */
 #define MK_OPT_EARLY_POLL_SHIFT   1  /* consumers stop watching a dependency counter and poll the data cells
                                       * themselves once it is within target >> shift of its target; 31 = never */
@@ -324,6 +322,32 @@ int mk_gemv_static(const void *w_bf16, const void *packed, const void *scales, c
 int32_t mk_linear_batched_splits(int32_t n, int32_t k, int32_t sm_count);
 int mk_linear_batched(const void *w_bf16, const void *x_bf16, void *y_bf16, float *partials,
                       int32_t n, int32_t k, int32_t batch, int32_t splits, int32_t *error_word, void *stream);
+
+/*
+ * The same linear with NVFP4 operands on both sides (tcgen05.mma
+ * kind::mxf4nvf4, block scale 16): E2M1 codes two per byte, one UE4M3 scale per
+ * 16 consecutive k, applied by the tensor core; y = bf16(acc * w_tensor_scale *
+ * x_tensor_scale).  Stands in for the reference's in-VM linear and its
+ * activation quantiser, include/ops/nvfp4_linear.cuh:52-173 and :174-237
+ * (v = x / tensor_scale, scale = e4m3(max(amax / 6, 2^-9)), code = e2m1(v / scale)).
+ *
+ * mk_nvfp4_quantize_native quantises a bf16 matrix [rows, k] (k a multiple of
+ * 64) into packed [rows, k/2] and block scales in the layout the tensor core
+ * reads ("native": 512-byte atoms of 128 rows x 4 k-groups, byte
+ * (r % 32) * 16 + (r % 128 / 32) * 4 + g % 4 inside atom (r / 128, g / 4);
+ * reference tools/analysis/nvfp4/mixed_format.py:9).  The scale buffer holds
+ * mk_nvfp4_native_scale_bytes(rows, k) bytes; the caller zeroes it once, so
+ * that rows beyond `rows` in the last atom hold scale 0.  Use it for weights
+ * (once) and for the activation panel (every step).
+ * mk_linear_batched_nvfp4: k a multiple of 256 (and of 256 * splits).
+ */
+int64_t mk_nvfp4_native_scale_bytes(int32_t rows, int32_t k);
+int mk_nvfp4_quantize_native(const void *input_bf16, void *packed, void *scales_native, int32_t rows, int32_t k,
+                             float tensor_scale, void *stream);
+int mk_linear_batched_nvfp4(const void *w_packed, const void *w_scales_native, float w_tensor_scale,
+                            const void *x_packed, const void *x_scales_native, float x_tensor_scale,
+                            void *y_bf16, float *partials, int32_t n, int32_t k, int32_t batch, int32_t splits,
+                            int32_t *error_word, void *stream);
 
 /*
  * Batched decode: one step for 1..128 sequences, each at its own position.

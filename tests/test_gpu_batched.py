@@ -127,3 +127,54 @@ def test_two_layer_model_independent_cache_lengths(batch):
         tokens = torch.tensor(want, dtype=torch.int32)
         pos = pos + 1
     dec.close()
+
+
+@pytest.mark.parametrize("rows,k", [(128, 256), (37, 512), (300, 2048)])
+def test_native_quantiser_is_bit_exact(rows, k):
+    """Codes and scale bytes equal the numpy oracle's (oracle/nvfp4.py); the
+    scale bytes sit in the tensor core's 512-byte atoms."""
+    import numpy as np
+
+    from oracle import nvfp4 as oracle
+    from thor_megakernels_b200 import batched
+
+    torch.manual_seed(rows + k)
+    x = torch.randn(rows, k).bfloat16()
+    x[0, :32] = 0
+    q = batched.quantize_native(x.cuda())
+    ts = oracle.tensor_scale_for(x.abs().max().item())
+    assert q.tensor_scale == float(ts)
+    packed, scales, _ = oracle.quantize(x.float().numpy(), ts)
+    assert np.array_equal(q.packed.cpu().numpy(), packed)
+    assert np.array_equal(q.canonical_scales().cpu().numpy(), scales)
+    # rows of the last atom beyond `rows` keep scale 0
+    native = q.scales.cpu().numpy().reshape(-1, k // 64, 32, 4, 4)
+    r = rows  # first row that does not exist
+    if r % 128:
+        assert native[r // 128, :, r % 32, (r % 128) // 32, :].sum() == 0
+
+
+@pytest.mark.parametrize("n,k", [(128, 256), (256, 1024), (3072, 2048), (2048, 8192), (1000, 2048)])
+@pytest.mark.parametrize("batch", [16, 64, 128, 37])
+def test_block_scaled_nvfp4_linear(n, k, batch):
+    """tcgen05 block-scaled NVFP4 linear against the oracle: both operands
+    decoded with the numpy oracle's decoder, exact (float64) dot products, one
+    bf16 rounding.  Tolerance: relative L2 <= 1e-3 (the reference's gate,
+    tools/analysis/nvfp4/check.py:43) and the element band."""
+    import numpy as np
+
+    from oracle import nvfp4 as oracle
+    from thor_megakernels_b200 import batched
+
+    gen = torch.Generator(device="cuda").manual_seed(n + k + batch)
+    w = (torch.randn(n, k, device="cuda", generator=gen) * 0.02).bfloat16()
+    x = torch.randn(batch, k, device="cuda", generator=gen).bfloat16()
+    qw, qx = batched.quantize_native(w), batched.quantize_native(x)
+    got = batched.linear_nvfp4(qw, qx)
+    batched.check_errors()
+    dw = oracle.dequantize(qw.packed.cpu().numpy(), qw.canonical_scales().cpu().numpy(), qw.tensor_scale).astype(np.float64)
+    dx = oracle.dequantize(qx.packed.cpu().numpy(), qx.canonical_scales().cpu().numpy(), qx.tensor_scale).astype(np.float64)
+    want = torch.from_numpy(dx @ dw.T).float().bfloat16().float()
+    assert got.shape == (batch, n)
+    assert rel_l2(got.float().cpu(), want) <= 1e-3
+    assert_close("nvfp4 linear", got, want)

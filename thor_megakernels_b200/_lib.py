@@ -27,7 +27,6 @@ MK_OPT_EARLY_POLL_SHIFT = 1
 MK_OPT_MAX_INFLIGHT_TILES = 2
 MK_OPT_DOWN_FOLD_LAST = 3
 MK_OPT_DOWN_FOLD_LOCAL = 4
-MK_OPT_L2_AHEAD_TILES = 5
 
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1
@@ -37,6 +36,7 @@ EXPORTED_SYMBOLS = [
     "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
     "mk_gemv_static", "mk_tp_init", "mk_tp_connect", "mk_gemv_workspace_bytes",
     "mk_linear_batched", "mk_linear_batched_splits",
+    "mk_nvfp4_native_scale_bytes", "mk_nvfp4_quantize_native", "mk_linear_batched_nvfp4",
     "mk_batched_create", "mk_step_batched", "mk_batched_status", "mk_batched_destroy",
 ]
 
@@ -117,6 +117,10 @@ def load() -> C.CDLL:
     lib.mk_gemv_workspace_bytes.argtypes = [i32, i32]
     lib.mk_linear_batched.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
     lib.mk_linear_batched_splits.argtypes = [i32, i32, i32]
+    lib.mk_nvfp4_native_scale_bytes.argtypes = [i32, i32]
+    lib.mk_nvfp4_native_scale_bytes.restype = C.c_int64
+    lib.mk_nvfp4_quantize_native.argtypes = [vp, vp, vp, i32, i32, f32, vp]
+    lib.mk_linear_batched_nvfp4.argtypes = [vp, vp, f32, vp, vp, f32, vp, vp, i32, i32, i32, i32, vp, vp]
     lib.mk_batched_create.argtypes = [C.POINTER(MkModelDesc), i32, C.POINTER(vp)]
     lib.mk_step_batched.argtypes = [vp, vp, vp, i32, vp, vp]
     lib.mk_batched_status.argtypes = [vp, vp]
@@ -127,7 +131,8 @@ def load() -> C.CDLL:
     lib.mk_abi_sizeof.argtypes = [i32]
     lib.mk_set_option.argtypes = [vp, i32, C.c_int64]
     for name in EXPORTED_SYMBOLS:
-        if name not in ("mk_last_error", "mk_destroy", "mk_gemv_workspace_bytes", "mk_batched_destroy"):
+        if name not in ("mk_last_error", "mk_destroy", "mk_gemv_workspace_bytes", "mk_batched_destroy",
+                        "mk_nvfp4_native_scale_bytes"):
             getattr(lib, name).restype = C.c_int
     lib.mk_gemv_workspace_bytes.restype = C.c_int64
     return lib

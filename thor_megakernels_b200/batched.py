@@ -62,6 +62,58 @@ def linear(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = Non
     return y if splits == 1 else partials
 
 
+class Nvfp4Native:
+    """A matrix quantised to NVFP4 with its block scales in the tensor core's
+    native layout (``mk_nvfp4_quantize_native``)."""
+
+    def __init__(self, packed: torch.Tensor, scales: torch.Tensor, tensor_scale: float, rows: int, k: int):
+        self.packed, self.scales, self.tensor_scale, self.rows, self.k = packed, scales, float(tensor_scale), rows, k
+
+    def canonical_scales(self) -> torch.Tensor:
+        """The scale bytes as a row-major ``[rows, k/16]`` matrix (the layout of
+        the weight-only path and of the reference's ``canonical`` output)."""
+        groups = self.k // 16
+        atoms = self.scales.view((self.rows + 127) // 128, groups // 4, 32, 4, 4)   # [slab, g/4, r%32, r%128//32, g%4]
+        rows = atoms.permute(0, 3, 2, 1, 4).reshape(-1, groups)                     # [slab, quarter, r%32] -> row ; [g/4, g%4] -> g
+        return rows[: self.rows].contiguous()
+
+
+def quantize_native(x: torch.Tensor, tensor_scale: float | None = None) -> Nvfp4Native:
+    """bf16 ``[rows, k]`` (k a multiple of 64) -> NVFP4 codes + native-layout
+    block scales.  ``tensor_scale`` defaults to ``amax / (6 * 448)`` as for weights."""
+    if x.device.type != "cuda" or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.ndim != 2:
+        raise ValueError("x must be a contiguous 2-D bf16 CUDA tensor")
+    rows, k = x.shape
+    lib = _lib.load()
+    if tensor_scale is None:
+        from .nvfp4 import tensor_scale_for
+
+        tensor_scale = tensor_scale_for(x)
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.zeros(max(1, int(lib.mk_nvfp4_native_scale_bytes(rows, k))), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.mk_nvfp4_quantize_native(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), rows, k, float(tensor_scale),
+                                                _stream(x)))
+    return Nvfp4Native(packed, scales, tensor_scale, rows, k)
+
+
+def linear_nvfp4(weight: Nvfp4Native, x: Nvfp4Native, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``y[b, n] = bf16(ts_w * ts_x * sum_k w[n, k] x[b, k])`` with both operands in
+    NVFP4, the block scales applied by the tensor core."""
+    if weight.k != x.k:
+        raise ValueError(f"x has {x.k} columns, weight has {weight.k}")
+    lib = _lib.load()
+    dev = x.packed.device
+    y = out if out is not None else torch.empty((x.rows, weight.rows), dtype=torch.bfloat16, device=dev)
+    err = _error_word(dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.mk_linear_batched_nvfp4(weight.packed.data_ptr(), weight.scales.data_ptr(), weight.tensor_scale,
+                                               x.packed.data_ptr(), x.scales.data_ptr(), x.tensor_scale, y.data_ptr(), None,
+                                               weight.rows, weight.k, x.rows, 1, err.data_ptr(),
+                                               torch.cuda.current_stream(dev).cuda_stream))
+    return y
+
+
 class BatchedDecoder:
     """Greedy decode of up to 128 sequences per step, each with its own cache
     length (``mk_batched_create`` / ``mk_step_batched``).

@@ -46,7 +46,10 @@ __global__ void embed_kernel(const bf16 *__restrict__ embed, const int *__restri
 // One CTA per sequence.  If a linear result is given (`add`), first the
 // interpreter's residual add  hidden[b] = bf16(hidden[b] + bf16(linear[b])),
 // then normed[b] = w * bf16(hidden[b] * rstd) with fp32 statistics.  `normed`
-// may be null (residual update only).
+// may be null (residual update only).  With lin.group > 0 every `group`
+// consecutive split-K partials form one addend that is rounded and added on
+// its own: the down projection's 2048-column slices, which the interpreter adds
+// one after the other (python_vm.py:59-80).
 __global__ void __launch_bounds__(kNormThreads)
 residual_norm_kernel(bf16 *__restrict__ hidden, const LinOut lin, int add, const bf16 *__restrict__ weight,
                      bf16 *__restrict__ normed, int hidden_size, float eps) {
@@ -57,7 +60,15 @@ residual_norm_kernel(bf16 *__restrict__ hidden, const LinOut lin, int add, const
     for (int i = threadIdx.x; i < hidden_size; i += kNormThreads) {
         float h = __bfloat162float(hidden[(size_t)b * hidden_size + i]);
         if (add) {
-            h = round_bf16(h + lin_value(lin, b, i));
+            if (lin.partials != nullptr && lin.group > 0) {
+                for (int s0 = 0; s0 < lin.splits; s0 += lin.group) {
+                    float total = 0.f;
+                    for (int sp = s0; sp < s0 + lin.group; ++sp) total += lin.partials[((size_t)sp * lin.batch + b) * lin.n + i];
+                    h = round_bf16(h + round_bf16(total * lin.scale));
+                }
+            } else {
+                h = round_bf16(h + lin_value(lin, b, i));
+            }
             hidden[(size_t)b * hidden_size + i] = __float2bfloat16_rn(h);
         }
         row[i] = h;

@@ -14,6 +14,7 @@ struct LinOut {
     const float *partials;
     int splits, batch, n;
     float scale;
+    int group;  // residual adds only: consecutive splits that form one bf16-rounded addend (0: all of them)
 };
 
 }  // namespace bo

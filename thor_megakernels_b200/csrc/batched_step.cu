@@ -44,6 +44,7 @@ struct BatchedHandle {
     int qkv_rows = 0;
     // split-K factor per linear
     int s_qkv = 1, s_o = 1, s_up = 1, s_down = 1;
+    int down_group = 0;  // split-K partials of the down projection per 2048-column slice (0: no slice structure)
     // workspace (one cudaMalloc)
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
@@ -96,6 +97,16 @@ extern "C" int mk_batched_create(const MkModelDesc *d, int32_t max_batch, void *
     h->s_o = mk_linear_batched_splits(H, qd, h->sms);
     h->s_up = mk_linear_batched_splits(inter, H, h->sms);
     h->s_down = mk_linear_batched_splits(H, inter, h->sms);
+    if (inter % 2048 == 0) {
+        // Split the down projection along the interpreter's 2048-column slices (each cut further
+        // into 1, 2 or 4 pieces while SMs would otherwise idle), so that the residual add can round
+        // and add slice by slice as the interpreter does.
+        const int slices = inter / 2048, slabs = (H + 127) / 128;
+        int pieces = 1;
+        while (slabs * slices * pieces < h->sms && pieces < 4) pieces *= 2;
+        h->s_down = slices * pieces;
+        h->down_group = pieces;
+    }
     const size_t B = max_batch;
     const size_t part_a = (size_t)std::max(std::max(h->s_qkv * h->qkv_rows, h->s_o * H), std::max(h->s_up * inter, h->s_down * H));
     const size_t part_b = (size_t)h->s_up * inter;
@@ -135,6 +146,7 @@ extern "C" int mk_step_batched(void *handle, const int32_t *tokens_in, const int
     auto result = [&](bf16 *y, float *partials, int n, int splits) {
         bo::LinOut o;
         o.y = y; o.partials = splits > 1 ? partials : nullptr; o.splits = splits; o.batch = batch; o.n = n; o.scale = 1.0f;
+        o.group = 0;
         return o;
     };
     auto linear = [&](const bf16 *w, const bf16 *x, bf16 *y, float *partials, int n, int k, int splits) {
@@ -174,6 +186,7 @@ extern "C" int mk_step_batched(void *handle, const int32_t *tokens_in, const int
         // down_proj; its residual add happens in the next norm
         MK_TRY(linear(down_w + (size_t)l * H * inter, h->act, h->qkv_y, h->part_a, H, inter, h->s_down));
         down_out = result(h->qkv_y, h->part_a, H, h->s_down);
+        down_out.group = h->down_group;
     }
     MK_TRY(launch_residual_norm(hidden, down_out, 1, (const bf16 *)d.lm_head_norm_w, h->normed, batch, H, d.rms_norm_eps, st));
     MK_TRY(linear((const bf16 *)d.lm_head_w, h->normed, (bf16 *)d.logits, nullptr, d.vocab_size, H, 1));

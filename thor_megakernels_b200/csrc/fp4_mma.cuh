@@ -86,9 +86,7 @@ __device__ __forceinline__ void fp4_rows_mma(float (&acc)[4], const uint4 (&code
                             codes_g[1].x, codes_g[1].y, codes_g[1].z, codes_g[1].w};
     const uint32_t wh[8] = {codes_h[0].x, codes_h[0].y, codes_h[0].z, codes_h[0].w,
                             codes_h[1].x, codes_h[1].y, codes_h[1].z, codes_h[1].w};
-    // Four accumulators: consecutive MMAs never wait for one another's result
-    // (a chain of 16 dependent MMAs would cost more than decoding their operands).
-    float acc1[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f}, acc3[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc2[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the chain of dependent MMAs
 #pragma unroll
     for (int blk = 0; blk < 4; ++blk) {  // one 16-column scale block = 8 code bytes = 2 words
         const uint32_t sg = e4m3_to_f16x2_dup(sc_g >> (8 * blk));
@@ -105,15 +103,13 @@ __device__ __forceinline__ void fp4_rows_mma(float (&acc)[4], const uint4 (&code
                 e2m1x4_to_f16x4(ch, ch4, pair, h01, h23);
                 const uint32_t a0 = hmul2_bits(g01, sg), a2 = hmul2_bits(g23, sg);
                 const uint32_t a1 = hmul2_bits(h01, sh), a3 = hmul2_bits(h23, sh);
-                if ((i & 3) == 0) mma_f16_16816(acc, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
-                else if ((i & 3) == 1) mma_f16_16816(acc1, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
-                else if ((i & 3) == 2) mma_f16_16816(acc2, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
-                else mma_f16_16816(acc3, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
+                if (i & 1) mma_f16_16816(acc2, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
+                else mma_f16_16816(acc, a0, a1, a2, a3, xh[2 * i], xh[2 * i + 1]);
             }
         }
     }
 #pragma unroll
-    for (int r = 0; r < 4; ++r) acc[r] += (acc1[r] + acc2[r]) + acc3[r];
+    for (int r = 0; r < 4; ++r) acc[r] += acc2[r];
 }
 
 // Same, with the activation operand kept as eight 16-byte vectors.

@@ -25,12 +25,25 @@
 // the epilogue writes fp32 partial sums [split, batch, n] for the caller's next
 // kernel to add in split order.
 //
+// NVFP4 variant (kind::mxf4nvf4, block16): both operands are E2M1 codes, two per
+// byte, with one UE4M3 scale per 16 consecutive K (reference
+// include/ops/nvfp4_linear.cuh:52-173).  A stage then covers 256 columns of K
+// (still one 128-byte swizzle row), and carries the 128 x 16 block scales of the
+// weight slab and of the activation panel (2 KiB each, stored in global memory
+// in the 512-byte atoms the tensor core reads: 32 rows x 16 bytes, byte
+// (r % 32) * 16 + (r % 128 / 32) * 4 + g % 4 for row r and K group g).  Before a
+// stage's four K=64 MMAs the issuing thread copies the scales from shared to
+// tensor memory (tcgen05.cp 32x128b.warpx4); the MMA applies them.  The epilogue
+// multiplies by the two fp32 tensor scales.
+//
 // Every wait is bounded: on expiry the CTA sets an error word, skips the rest of
 // its work, waits (bounded) for copies in flight, frees its tensor memory and
 // returns.
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -52,14 +65,19 @@ constexpr int kATileBytes = kSlabRows * kBlockK * 2;  // 16 KiB
 constexpr int kMaxBatch = 128;
 constexpr long long kWaitCycles = 2000000000ll;       // about a second
 
+constexpr int kSfBytes = 2048;          // block scales of 128 rows x 256 columns (4 atoms of 512 bytes)
+
+template <bool FP4>
 struct __align__(1024) Stage {
     uint8_t a[kATileBytes];
     uint8_t b[kMaxBatch * kBlockK * 2];
+    uint8_t sfa[FP4 ? kSfBytes : 16];
+    uint8_t sfb[FP4 ? kSfBytes : 16];
 };
 
-template <int STAGES>
+template <int STAGES, bool FP4>
 struct Smem {
-    Stage stage[STAGES];
+    Stage<FP4> stage[STAGES];
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];
@@ -70,7 +88,10 @@ struct Smem {
 
 struct Params {
     int n, k, batch, batch_pad;   // batch_pad: MMA N, power of two in 16..128
-    int splits, kblocks_per_split;
+    int splits, kblocks_per_split;  // K blocks: 64 columns (bf16) or 256 columns (NVFP4)
+    int kblocks;                  // K blocks of the whole matrix
+    const uint8_t *sfa, *sfb;     // NVFP4: block scales of weights / activations in 512-byte atoms
+    float alpha;                  // NVFP4: weight tensor scale x activation tensor scale
     int slabs;
     bf16 *y;                      // [batch, n] when splits == 1
     float *partials;              // [splits, batch, n] otherwise
@@ -121,6 +142,30 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
         : "memory");
 }
 
+// kind::mxf4nvf4 instruction descriptor: E2M1 x E2M1, UE4M3 scales per 16, fp32 accumulate, M = 128, K = 64.
+__device__ __forceinline__ uint32_t idesc_nvfp4(int n) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kSlabRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_nvfp4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                           uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// One 512-byte scale atom (32 rows x 16 bytes, dense) from shared to tensor memory:
+// lane L of every 32-lane quarter receives row L % 32, i.e. 4 columns of 32 bits.
+__device__ __forceinline__ void copy_scales_to_tmem(uint32_t taddr, const void *atom) {
+    const uint64_t addr = smem_addr(atom);
+    // no swizzle, 8-row groups 128 bytes apart, one 16-byte column
+    const uint64_t desc = ((addr >> 4) & 0x3fffull) | (8ull << 32) | (1ull << 46);
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
 // Arrives on the barrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -139,15 +184,21 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int STAGES>
+template <int STAGES, bool FP4>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
     extern __shared__ uint8_t smem_raw[];
-    Smem<STAGES> &s = *reinterpret_cast<Smem<STAGES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    Smem<STAGES, FP4> &s = *reinterpret_cast<Smem<STAGES, FP4> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // K columns per stage and their bytes in a 128-byte swizzle row: 64 bf16 or 256 four-bit codes
+    constexpr int kStageK = FP4 ? 256 : kBlockK;
+    static_assert(kStageK == 64 || kStageK == 256, "one 128-byte swizzle row per stage");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *failed = &s.failed;
     const uint32_t acc_cols = (uint32_t)p.batch_pad;       // fp32 columns of one accumulator
-    const uint32_t tmem_cols = acc_cols * 2 < 32 ? 32 : acc_cols * 2;
+    // two accumulators, then (NVFP4) 16 columns of weight scales and 16 of activation scales
+    const uint32_t sf_base = acc_cols * 2;
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < acc_cols * 2 + (FP4 ? 32u : 0u)) tmem_cols *= 2;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -172,7 +223,7 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
     // work items of this CTA: (slab, split) pairs, dealt round robin
     const int items = p.slabs * p.splits;
-    const int stage_tx = kATileBytes + p.batch_pad * kBlockK * 2;
+    const int stage_tx = kATileBytes + p.batch_pad * kBlockK * 2 + (FP4 ? 2 * kSfBytes : 0);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -187,8 +238,14 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     if (!wait_bounded(&s.empty[stage], phase ^ 1u, failed)) break;
                     filled |= 1u << stage;
                     mbar_arrive_expect_tx(&s.full[stage], stage_tx);
-                    tma_load_2d(s.stage[stage].a, &map_w, kb * kBlockK, slab * kSlabRows, &s.full[stage], stream_policy);
-                    tma_load_2d(s.stage[stage].b, &map_x, kb * kBlockK, 0, &s.full[stage], keep_policy);
+                    // x coordinate in elements of the map's type: bf16 columns, or bytes of packed codes (128 per stage)
+                    const int x = FP4 ? kb * 128 : kb * kBlockK;
+                    tma_load_2d(s.stage[stage].a, &map_w, x, slab * kSlabRows, &s.full[stage], stream_policy);
+                    tma_load_2d(s.stage[stage].b, &map_x, x, 0, &s.full[stage], keep_policy);
+                    if constexpr (FP4) {
+                        bulk_load(s.stage[stage].sfa, p.sfa + ((size_t)slab * p.kblocks + kb) * kSfBytes, kSfBytes, &s.full[stage], stream_policy);
+                        bulk_load(s.stage[stage].sfb, p.sfb + (size_t)kb * kSfBytes, kSfBytes, &s.full[stage], keep_policy);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -208,7 +265,7 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = idesc_bf16(p.batch_pad);
+            const uint32_t idesc = FP4 ? idesc_nvfp4(p.batch_pad) : idesc_bf16(p.batch_pad);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             for (int item = blockIdx.x; item < items && !*failed; item += gridDim.x) {
                 if (!wait_bounded(&s.acc_empty[acc], acc_phase ^ 1u, failed)) break;
@@ -221,9 +278,22 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     tcgen05_fence_after();
                     const uint64_t da = smem_desc_k_major_sw128(s.stage[stage].a);
                     const uint64_t db = smem_desc_k_major_sw128(s.stage[stage].b);
+                    if constexpr (FP4) {
+                        // this stage's scales: 4 atoms each for the weight slab and the activation panel
 #pragma unroll
-                    for (int ks = 0; ks < kBlockK / kUmmaK; ++ks)  // 32 bytes further along the swizzled row per K step
-                        umma_bf16(tmem_d, da + 2 * ks, db + 2 * ks, idesc, (kb | ks) != 0);
+                        for (int ks = 0; ks < 4; ++ks) {
+                            copy_scales_to_tmem(tmem_base + sf_base + 4 * ks, s.stage[stage].sfa + 512 * ks);
+                            copy_scales_to_tmem(tmem_base + sf_base + 16 + 4 * ks, s.stage[stage].sfb + 512 * ks);
+                        }
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)  // K = 64 codes = 32 bytes further along the swizzled row per step
+                            umma_nvfp4(tmem_d, da + 2 * ks, db + 2 * ks, idesc, (kb | ks) != 0, tmem_base + sf_base + 4 * ks,
+                                       tmem_base + sf_base + 16 + 4 * ks);
+                    } else {
+#pragma unroll
+                        for (int ks = 0; ks < kBlockK / kUmmaK; ++ks)  // 32 bytes further along the swizzled row per K step
+                            umma_bf16(tmem_d, da + 2 * ks, db + 2 * ks, idesc, (kb | ks) != 0);
+                    }
                     umma_commit(&s.empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -253,8 +323,9 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     for (int j = 0; j < 16; ++j) {
                         const int b = c0 + j;
                         if (b < p.batch) {
-                            if (p.splits == 1) p.y[(size_t)b * p.n + row] = __float2bfloat16_rn(__uint_as_float(v[j]));
-                            else p.partials[((size_t)split * p.batch + b) * p.n + row] = __uint_as_float(v[j]);
+                            const float value = FP4 ? __uint_as_float(v[j]) * p.alpha : __uint_as_float(v[j]);
+                            if (p.splits == 1) p.y[(size_t)b * p.n + row] = __float2bfloat16_rn(value);
+                            else p.partials[((size_t)split * p.batch + b) * p.n + row] = value;
                         }
                     }
                 }
@@ -295,26 +366,122 @@ static EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// bf16 matrix [rows, k] row-major -> boxes of 64 columns x box_rows rows, 128-byte swizzle
-static bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+// Row-major matrix [rows, row_bytes] -> boxes of 128 bytes x box_rows rows, 128-byte swizzle.
+// bf16: 64 elements per box row; packed E2M1 codes are moved as bytes (256 codes per box row).
+static bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, bool bytes) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
-    const cuuint64_t dims[2] = {k, rows};
-    const cuuint64_t strides[1] = {k * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_rows};
+    const cuuint64_t dims[2] = {bytes ? row_bytes : row_bytes / 2, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {bytes ? 128u : 64u, box_rows};
     const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    return fn(map, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
+              strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-constexpr int kStages = 6;
+constexpr int kStagesBf16 = 6;   // 6 x 32 KiB
+constexpr int kStagesFp4 = 5;    // 5 x 36 KiB
+
+template <bool FP4>
+static int launch(const void *w, const void *x, const uint8_t *sfa, const uint8_t *sfb, float alpha, void *y, float *partials,
+                  int n, int k, int batch, int splits, int *error_word, cudaStream_t stream, const char *who) {
+    constexpr int kStages = FP4 ? kStagesFp4 : kStagesBf16;
+    constexpr int kStageK = FP4 ? 256 : kBlockK;
+    char msg[256];
+    if (!w || !x || n <= 0 || k <= 0 || batch < 1 || batch > kMaxBatch || splits < 1 || !error_word || (splits == 1 ? !y : !partials) ||
+        (FP4 && (!sfa || !sfb))) {
+        snprintf(msg, sizeof(msg), "%s: null pointer, batch outside 1..128 or splits < 1", who);
+        set_last_error(msg);
+        return MK_ERR_BAD_ARGUMENT;
+    }
+    if (k % kStageK || (k / kStageK) % splits || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) ||
+        (FP4 && ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)))) {
+        snprintf(msg, sizeof(msg), "%s: k=%d must be a multiple of %d and of %d*splits (%d); pointers 16-byte aligned", who, k, kStageK,
+                 kStageK, splits);
+        set_last_error(msg);
+        return MK_ERR_UNSUPPORTED;
+    }
+    int batch_pad = 16;
+    while (batch_pad < batch) batch_pad *= 2;
+    const uint64_t row_bytes = FP4 ? (uint64_t)k / 2 : (uint64_t)k * 2;
+    CUtensorMap map_w, map_x;
+    // rows beyond n / batch are outside the tensor: TMA fills them with zeros
+    if (!make_map(&map_w, w, (uint64_t)n, row_bytes, kSlabRows, FP4) || !make_map(&map_x, x, (uint64_t)batch, row_bytes, (uint32_t)batch_pad, FP4)) {
+        snprintf(msg, sizeof(msg), "%s: cuTensorMapEncodeTiled failed (driver without tensor-map support?)", who);
+        set_last_error(msg);
+        return MK_ERR_UNSUPPORTED;
+    }
+    Params p;
+    p.n = n; p.k = k; p.batch = batch; p.batch_pad = batch_pad;
+    p.kblocks = k / kStageK;
+    p.splits = splits; p.kblocks_per_split = p.kblocks / splits;
+    p.slabs = (n + kSlabRows - 1) / kSlabRows;
+    p.y = (bf16 *)y; p.partials = partials; p.error = error_word;
+    p.sfa = sfa; p.sfb = sfb; p.alpha = alpha;
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return (int)e;
+    const size_t smem = sizeof(Smem<kStages, FP4>) + 1024;
+    static bool configured[64] = {};
+    if (device < 64 && !configured[device]) {
+        e = cudaFuncSetAttribute(linear_batched_kernel<kStages, FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured[device] = true;
+    }
+    const int items = p.slabs * splits;
+    const int grid = items < sms ? items : sms;
+    linear_batched_kernel<kStages, FP4><<<grid, kThreads, smem, stream>>>(map_w, map_x, p);
+    return (int)cudaGetLastError();
+}
+
+// One thread quantises 16 consecutive values of a row (the arithmetic of the
+// weight quantiser, nvfp4.cu: v = x / tensor_scale, scale = e4m3(max(amax / 6, 2^-9)),
+// code = e2m1(v / scale)); codes go to packed [rows, k/2], the scale byte into the
+// 512-byte atoms the tensor core reads.
+__global__ void quantize_native_kernel(const bf16 *__restrict__ input, uint8_t *__restrict__ packed, uint8_t *__restrict__ sf,
+                                       int rows, int k, float tensor_scale) {
+    const int groups_per_row = k / 16;
+    const long long grp = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (grp >= (long long)rows * groups_per_row) return;
+    const int r = (int)(grp / groups_per_row), g = (int)(grp % groups_per_row);
+    const uint4 *src = reinterpret_cast<const uint4 *>(input + grp * 16);
+    float v[16];
+    {
+        float a[8], b[8];
+        unpack8(__ldg(src), a);
+        unpack8(__ldg(src + 1), b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[i] = a[i] / tensor_scale;
+            v[8 + i] = b[i] / tensor_scale;
+        }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const __nv_fp8_e4m3 scale_bits(fmaxf(amax / 6.f, 1.f / 512.f));
+    const float scale = float(scale_bits);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t q0 = (uint32_t)__nv_cvt_float_to_fp4(v[2 * i] / scale, __NV_E2M1, cudaRoundNearest) & 0xFu;
+        const uint32_t q1 = (uint32_t)__nv_cvt_float_to_fp4(v[2 * i + 1] / scale, __NV_E2M1, cudaRoundNearest) & 0xFu;
+        const uint32_t byte = q0 | (q1 << 4);
+        if (i < 4) lo |= byte << (8 * i);
+        else hi |= byte << (8 * (i - 4));
+    }
+    *reinterpret_cast<uint2 *>(packed + grp * 8) = make_uint2(lo, hi);
+    const size_t atom = ((size_t)(r / 128) * (groups_per_row / 4) + g / 4) * 512;
+    sf[atom + (r % 32) * 16 + ((r % 128) / 32) * 4 + (g % 4)] = scale_bits.__x;
+}
 
 }  // namespace lb
 }  // namespace mk
 
 extern "C" int32_t mk_linear_batched_splits(int32_t n, int32_t k, int32_t sm_count) {
-    // Enough (slab, split) items to give every SM work, while a split keeps at least 8 K blocks.
+    // Enough (slab, split) items to give every SM work, while a split keeps at least 8 K blocks of 64.
     if (n <= 0 || k <= 0 || sm_count <= 0) return 1;
     const int slabs = (n + mk::lb::kSlabRows - 1) / mk::lb::kSlabRows, kblocks = k / mk::lb::kBlockK;
     int splits = 1;
@@ -324,45 +491,32 @@ extern "C" int32_t mk_linear_batched_splits(int32_t n, int32_t k, int32_t sm_cou
 
 extern "C" int mk_linear_batched(const void *w_bf16, const void *x_bf16, void *y_bf16, float *partials, int32_t n, int32_t k,
                                  int32_t batch, int32_t splits, int32_t *error_word, void *stream) {
-    using namespace mk;
-    using namespace mk::lb;
-    char msg[256];
-    if (!w_bf16 || !x_bf16 || n <= 0 || k <= 0 || batch < 1 || batch > kMaxBatch || splits < 1 || !error_word ||
-        (splits == 1 ? !y_bf16 : !partials)) {
-        set_last_error("mk_linear_batched: null pointer, batch outside 1..128 or splits < 1");
+    return mk::lb::launch<false>(w_bf16, x_bf16, nullptr, nullptr, 1.0f, y_bf16, partials, n, k, batch, splits, error_word,
+                                 (cudaStream_t)stream, "mk_linear_batched");
+}
+
+extern "C" int64_t mk_nvfp4_native_scale_bytes(int32_t rows, int32_t k) {
+    if (rows <= 0 || k <= 0 || k % 64) return 0;
+    return (int64_t)((rows + 127) / 128) * (k / 64) * 512;
+}
+
+extern "C" int mk_nvfp4_quantize_native(const void *input_bf16, void *packed, void *scales_native, int32_t rows, int32_t k,
+                                        float tensor_scale, void *stream) {
+    if (!input_bf16 || !packed || !scales_native || rows <= 0 || k <= 0 || (k % 64) != 0 || !(tensor_scale > 0.f)) {
+        mk::set_last_error("mk_nvfp4_quantize_native: null pointer, k not a multiple of 64 or non-positive scale");
         return MK_ERR_BAD_ARGUMENT;
     }
-    if (k % kBlockK || (k / kBlockK) % splits || (reinterpret_cast<uintptr_t>(w_bf16) & 15) || (reinterpret_cast<uintptr_t>(x_bf16) & 15)) {
-        snprintf(msg, sizeof(msg), "mk_linear_batched: k=%d must be a multiple of 64 and of 64*splits (%d); pointers 16-byte aligned", k, splits);
-        set_last_error(msg);
-        return MK_ERR_UNSUPPORTED;
-    }
-    int batch_pad = 16;
-    while (batch_pad < batch) batch_pad *= 2;
-    CUtensorMap map_w, map_x;
-    // rows beyond n / batch are outside the tensor: TMA fills them with zeros
-    if (!make_map(&map_w, w_bf16, (uint64_t)n, (uint64_t)k, kSlabRows) || !make_map(&map_x, x_bf16, (uint64_t)batch, (uint64_t)k, (uint32_t)batch_pad)) {
-        set_last_error("mk_linear_batched: cuTensorMapEncodeTiled failed (driver without tensor-map support?)");
-        return MK_ERR_UNSUPPORTED;
-    }
-    Params p;
-    p.n = n; p.k = k; p.batch = batch; p.batch_pad = batch_pad;
-    p.splits = splits; p.kblocks_per_split = (k / kBlockK) / splits;
-    p.slabs = (n + kSlabRows - 1) / kSlabRows;
-    p.y = (bf16 *)y_bf16; p.partials = partials; p.error = error_word;
-    int device = 0, sms = 0;
-    cudaError_t e = cudaGetDevice(&device);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    if (e != cudaSuccess) return (int)e;
-    const size_t smem = sizeof(Smem<kStages>) + 1024;
-    static bool configured[64] = {};
-    if (device < 64 && !configured[device]) {
-        e = cudaFuncSetAttribute(linear_batched_kernel<kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured[device] = true;
-    }
-    const int items = p.slabs * splits;
-    const int grid = items < sms ? items : sms;
-    linear_batched_kernel<kStages><<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_w, map_x, p);
+    const long long groups = (long long)rows * (k / 16);
+    const int threads = 256;
+    mk::lb::quantize_native_kernel<<<(unsigned)((groups + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
+        (const mk::bf16 *)input_bf16, (uint8_t *)packed, (uint8_t *)scales_native, rows, k, tensor_scale);
     return (int)cudaGetLastError();
+}
+
+extern "C" int mk_linear_batched_nvfp4(const void *w_packed, const void *w_scales_native, float w_tensor_scale, const void *x_packed,
+                                       const void *x_scales_native, float x_tensor_scale, void *y_bf16, float *partials,
+                                       int32_t n, int32_t k, int32_t batch, int32_t splits, int32_t *error_word, void *stream) {
+    return mk::lb::launch<true>(w_packed, x_packed, (const uint8_t *)w_scales_native, (const uint8_t *)x_scales_native,
+                                w_tensor_scale * x_tensor_scale, y_bf16, partials, n, k, batch, splits, error_word,
+                                (cudaStream_t)stream, "mk_linear_batched_nvfp4");
 }

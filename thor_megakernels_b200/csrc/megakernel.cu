@@ -103,7 +103,6 @@ struct Params {
     float attn_scale, eps;
     long long spin_cycles;
     int max_inflight;  // weight tiles a loader keeps in flight
-    int l2_ahead;      // weight tiles beyond the ring that a loader asks L2 to fetch ahead of time (0: none)
     int early_shift;  // consumers start polling cells once a counter is within expected >> early_shift of its target (31: never early)
     int o_cols, o_chunks, o_width;  // output projection: input columns (Hq*D), tiles per row block, columns per tile
     int down_width;   // columns of one down-projection slice (multiple of 256, at most 2048)
@@ -298,10 +297,34 @@ struct F8 { float v[8]; };
 // footprint of the streaming code around the (almost always successful) first try.
 __device__ __noinline__ uint4 load8_slow(const Params &p, Smem &s, const unsigned long long *cells, uint32_t tag,
                                          int opcode, int slot) {
+    // Two probes stay in flight, issued about half an L2 round trip apart, and a new one
+    // replaces each probe that comes back without the tag: the cells are looked at
+    // twice per round trip instead of once, which shortens the time between a
+    // producer's store becoming visible and this thread noticing it.
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     Deadline d = start_deadline();
-    while (keep_waiting(p, s, d, opcode, slot, 0))
-        if (try_load8(cells, tag, out)) break;
+    ulonglong2 a0 = ld_tagged2(cells), a1 = ld_tagged2(cells + 2);
+    __nanosleep(250);
+    ulonglong2 b0 = ld_tagged2(cells), b1 = ld_tagged2(cells + 2);
+    while (true) {
+        if (tag_ok(a0.x, tag) & tag_ok(a0.y, tag) & tag_ok(a1.x, tag) & tag_ok(a1.y, tag)) {
+            out = make_uint4(tag_payload(a0.x), tag_payload(a0.y), tag_payload(a1.x), tag_payload(a1.y));
+            break;
+        }
+        a0 = b0; a1 = b1;
+        b0 = ld_tagged2(cells); b1 = ld_tagged2(cells + 2);
+        if ((++d.it & 15u) == 0) {
+            if (aborted(s)) break;
+            if (ld_relaxed_gpu(&p.status[7]) != 0) {
+                *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+                break;
+            }
+            if (clock64() - d.t0 > p.spin_cycles) {
+                report_failure(p, s, kFailData, opcode, slot, 0, 0);
+                break;
+            }
+        }
+    }
     return out;
 }
 
@@ -370,10 +393,23 @@ __device__ __forceinline__ const int *instruction_at(const Params &p, int slot) 
     return p.instructions + ((size_t)blockIdx.x * p.queue_len + slot) * kInstrWords;
 }
 
-// Opcode of the instruction in `slot` (0 beyond the queue).  Every role reads the
-// NEXT instruction's opcode while it still works on the current one: the load
-// brings the instruction's 128-byte line into this SM's L1, so that by the time
-// the role gets there neither the opcode nor the operand words cost a trip to L2.
+// The 32 words of an instruction, one per lane of a warp.  Every warp fetches the
+// NEXT instruction (one 128-byte load) while it still works on the current one
+// and reads fields with a shuffle, so that getting to an instruction costs no
+// trip to L2 (about a microsecond while weights are streaming).
+struct InsWords {
+    int w;  // this lane's word
+    // word k, the same for all lanes; every lane of the warp must call this together
+    __device__ __forceinline__ int operator[](int k) const { return __shfl_sync(0xffffffffu, w, k); }
+};
+
+__device__ __forceinline__ InsWords fetch_instruction(const Params &p, int slot, int lane) {
+    InsWords iw;
+    iw.w = slot < p.queue_len ? __ldg(instruction_at(p, slot) + lane) : 0;
+    return iw;
+}
+
+// Single-thread variant (the loader): opcode of the instruction in `slot`, 0 beyond the queue.
 __device__ __forceinline__ int opcode_at(const Params &p, int slot) {
     return slot < p.queue_len ? __ldg(instruction_at(p, slot)) : 0;
 }
@@ -414,7 +450,10 @@ template <int NCH, bool FP4>
 struct TileCursor {
     int slot = -1;
     int op = 0;
-    int next_op = -1;       // opcode of slot + 1, loaded while the tiles of `slot` are being issued (-1: not loaded yet)
+    // words 0..4 of slot + 1, loaded while the tiles of `slot` are being issued (ahead.x < 0: not loaded yet)
+    int4 ahead = make_int4(-1, 0, 0, 0);
+    int ahead4 = 0;
+    int w1 = 0, w2 = 0, w3 = 0, w4 = 0;  // words 1..4 of the current instruction
     int idx = 0, cnt = 0;   // block position within the instruction
     int sub = 0, nsub = 1;  // tile position within the block
     int first_block = 0;
@@ -463,45 +502,54 @@ struct TileCursor {
             }
             if (++slot >= p.queue_len) return false;
             ins = instruction_at(p, slot);
-            op = next_op >= 0 ? next_op : __ldg(ins);
-            next_op = opcode_at(p, slot + 1);
+            if (ahead.x < 0) {
+                ahead = __ldg(reinterpret_cast<const int4 *>(ins));
+                ahead4 = __ldg(ins + 4);
+            }
+            op = ahead.x; w1 = ahead.y; w2 = ahead.z; w3 = ahead.w; w4 = ahead4;
+            if (slot + 1 < p.queue_len) {
+                ahead = __ldg(reinterpret_cast<const int4 *>(instruction_at(p, slot + 1)));
+                ahead4 = __ldg(instruction_at(p, slot + 1) + 4);
+            } else {
+                ahead = make_int4(0, 0, 0, 0);
+            }
             idx = 0; sub = 0; cnt = 0; nsub = NCH; col0 = 0; width = kChunkCols;
             const size_t hidden = p.hidden;
             switch (op) {
             case 1: {
-                const int layer = __ldg(ins + 1);
-                first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block;
+                const int layer = w1;
+                first_block = w2; cnt = w3 - first_block;
                 row_elems = hidden;
                 bind(p.qkv_w, p.q_qkv, layer, (size_t)p.qkv_rows * hidden, false);
                 break;
             }
             case 4: {
-                const int layer = __ldg(ins + 1);
-                first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block;
+                const int layer = w1;
+                first_block = w2; cnt = w3 - first_block;
                 row_elems = (size_t)p.o_cols;
                 nsub = p.o_chunks; width = p.o_width;
                 bind(p.o_w, p.q_o, layer, hidden * row_elems, false);
                 break;
             }
             case 5: {
-                const int layer = __ldg(ins + 1);
-                cnt = __ldg(ins + 2); nsub = 2 * NCH;  // up tiles, then gate tiles
+                const int layer = w1;
+                cnt = w2; nsub = 2 * NCH;  // up tiles, then gate tiles
                 row_elems = hidden;
                 bind(p.up_w, p.q_up, layer, (size_t)p.inter * hidden, false);
                 bind(p.gate_w, p.q_gate, layer, (size_t)p.inter * hidden, true);
                 break;
             }
             case 6: {
-                const int layer = __ldg(ins + 1);
-                first_block = __ldg(ins + 2); cnt = __ldg(ins + 3) - first_block; nsub = 1;
+                const int layer = w1;
+                first_block = w2; cnt = w3 - first_block; nsub = 1;
                 row_elems = p.inter;
                 width = p.down_width;
-                col0 = (size_t)__ldg(ins + 4) * width;
+                col0 = (size_t)w4 * width;
                 bind(p.down_w, p.q_down, layer, hidden * row_elems, false);
                 break;
             }
             case 7:
-                first_block = __ldg(ins + 1); cnt = __ldg(ins + 2) - first_block;
+                first_block = w1; cnt = w2 - first_block;
                 row_elems = hidden;
                 bind(p.lm_w, p.q_lm, 0, 0, false);
                 break;
@@ -523,31 +571,7 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
     TileCursor<NCH, FP4> tiles;
     Tile t;
     int last_slot = -1;
-    // Second cursor over the same queue, running up to l2_ahead tiles ahead of the
-    // fills: while the ring is full (its tiles wait for activations that are still
-    // being produced), HBM would otherwise sit idle; asking L2 for the tiles after
-    // the ring keeps it busy, and their later fills are served from L2.
-    TileCursor<NCH, FP4> ahead;
-    Tile ta;
-    int filled = 0, hinted = 0;
-    bool more_ahead = p.l2_ahead > 0;
     while (tiles.next(p, t)) {
-        while (more_ahead && hinted < filled + Fmt<FP4>::stages + p.l2_ahead) {
-            more_ahead = ahead.next(p, ta);
-            if (!more_ahead) break;
-            if (++hinted <= filled + Fmt<FP4>::stages) continue;  // the ring itself covers these
-            if constexpr (FP4) {
-                for (int r = 0; r < kBlockRows; ++r) {
-                    bulk_prefetch_l2(ta.src + r * ta.stride_bytes, ta.width / 2);
-                    bulk_prefetch_l2(ta.scales + r * ta.scale_stride, ta.width / 16);
-                }
-            } else if (ta.stride_bytes == (size_t)ta.width * 2) {
-                bulk_prefetch_l2(ta.src, kBlockRows * ta.width * 2);  // rows are contiguous: one request
-            } else {
-                for (int r = 0; r < kBlockRows; ++r) bulk_prefetch_l2(ta.src + r * ta.stride_bytes, ta.width * 2);
-            }
-        }
-        ++filled;
         if (t.slot != last_slot) {
             if (last_slot >= 0) stamp(p, last_slot, kEvLastLoad, t_start);
             stamp(p, t.slot, kEvLoaderStart, t_start);
@@ -1123,18 +1147,18 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
     const bf16 *step_input = p.hidden_states;
     if (p.flags & MK_STEP_EMBED) step_input = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
 
-    int next_op = opcode_at(p, 0);
+    InsWords next_ins = fetch_instruction(p, 0, lane);
 #pragma unroll 1
     for (int slot = 0; slot < p.queue_len; ++slot) {
-        const int *ins = instruction_at(p, slot);
-        const int op = next_op;
-        next_op = opcode_at(p, slot + 1);  // in flight while this instruction runs
+        const InsWords ins = next_ins;
+        next_ins = fetch_instruction(p, slot + 1, lane);  // in flight while this instruction runs
+        const int op = ins[0];
         if (op == 0) continue;
         if (ctid == 0) stamp(p, slot, kEvConsumerStart, t_start);
         uint4 x[NCH][8];
         switch (op) {
         case 1: {
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
+            const int layer = ins[1], b0 = ins[2], b1 = ins[3];
             if (layer != p.first_layer) {
                 if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
                 consumer_wait(p, s, ctid, counter(p, layer - 1, 5, 0), p.down_total, op, slot);
@@ -1148,14 +1172,14 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             break;
         }
         case 2:
-            if (p.hd == 64) attention_partial<8>(p, s, ctid, tag, ins, slot, t_start);
-            else attention_partial<16>(p, s, ctid, tag, ins, slot, t_start);
+            if (p.hd == 64) attention_partial<8>(p, s, ctid, tag, instruction_at(p, slot), slot, t_start);
+            else attention_partial<16>(p, s, ctid, tag, instruction_at(p, slot), slot, t_start);
             break;
         case 3:
-            attention_reduction(p, s, ctid, tag, ins, slot, t_start);
+            attention_reduction(p, s, ctid, tag, instruction_at(p, slot), slot, t_start);
             break;
         case 4: {
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
+            const int layer = ins[1], b0 = ins[2], b1 = ins[3];
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, layer, 2, 0), p.hq, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
@@ -1165,7 +1189,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             break;
         }
         case 5: {
-            const int layer = __ldg(ins + 1), n = __ldg(ins + 2);
+            const int layer = ins[1], n = ins[2];
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, layer, 3, 0), p.hidden / kBlockRows, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
@@ -1179,7 +1203,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             break;
         }
         case 6: {
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
+            const int layer = ins[1], b0 = ins[2], b1 = ins[3], red = ins[4];
             if (p.down_local) {
                 // This queue holds the instructions of all column slices of rows
                 // [b0*16, b1*16) in the next down_slices slots (checked when the schedule
@@ -1189,6 +1213,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
                 // once instead of once per slice.  Loader and storer still see one
                 // instruction per slice.
                 const int S = p.down_slices, width = p.down_width;
+                const InsWords after_run = fetch_instruction(p, slot + S, lane);  // what follows the run
                 const int t = lane & 3;
                 const bool has_cols = ctid * 8 < width;  // narrower slices leave the upper threads without columns
                 const unsigned long long *silu = p.t_silu + ((size_t)layer * p.inter) / 2 + (ctid * 8) / 2;
@@ -1221,7 +1246,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
                     if (ctid == 0) stamp(p, slot + r, kEvLastUse, t_start);
                 }
                 slot += S - 1;  // the slices' instructions have been consumed
-                next_op = opcode_at(p, slot + 1);
+                next_ins = after_run;
                 continue;
             }
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
@@ -1236,7 +1261,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
             break;
         }
         case 7: {
-            const int b0 = __ldg(ins + 1), b1 = __ldg(ins + 2);
+            const int b0 = ins[1], b1 = ins[2];
             if (ctid == 0) stamp(p, slot, kEvAtWait, t_start);
             consumer_wait(p, s, ctid, counter(p, p.layers - 1, 5, 0), p.down_total, op, slot);
             if (ctid == 0) stamp(p, slot, kEvDoneWait, t_start);
@@ -1465,19 +1490,19 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
     const bool pair_writer = writer && (lane & 1) == 0;  // ... and write the cell of rows (lane, lane+1)
     int run_start = -1, run_layer = -1;                 // consecutive down-projection instructions of one layer
 
-    int next_op = opcode_at(p, 0);
+    InsWords next_ins = fetch_instruction(p, 0, lane);
 #pragma unroll 1
     for (int slot = 0; slot < p.queue_len; ++slot) {
-        const int *ins = instruction_at(p, slot);
-        const int op = next_op;
-        next_op = opcode_at(p, slot + 1);  // in flight while this instruction runs
+        const InsWords ins = next_ins;
+        next_ins = fetch_instruction(p, slot + 1, lane);  // in flight while this instruction runs
+        const int op = ins[0];
         if (op == 0) continue;
         if (lane == 0) stamp(p, slot, kEvStorerStart, t_start);
         switch (op) {
         case 1: {
             // bf16(matvec) -> RoPE in fp32 on Q and K rows -> bf16 store
             // (reference python_vm.py:196-248, llama.py:136-174)
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
+            const int layer = ins[1], b0 = ins[2], b1 = ins[3];
             const size_t cache_row = (((size_t)layer * p.kv_batch) * p.kv_len + p.pos) * (size_t)(p.hkv * D);
             // rotary factors depend only on the position: fetch those of the first
             // two blocks before the sums arrive
@@ -1534,7 +1559,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
         }
         case 4: {
             // residual[rows] = bf16(residual[rows] + bf16(matvec)) (reference python_vm.py:59-104)
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3);
+            const int layer = ins[1], b0 = ins[2], b1 = ins[3];
             // Residual stream entering this layer: the step input or the previous
             // layer's output.  It is upstream of this instruction, so it is fetched
             // (and waited for) before the sums arrive.
@@ -1570,10 +1595,10 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
         }
         case 5: {
             // bf16(bf16(silu(bf16 gate)) * bf16 up) (reference python_vm.py:146-165)
-            const int layer = __ldg(ins + 1), n = __ldg(ins + 2);
+            const int layer = ins[1], n = ins[2];
             const float ts_up = matrix_scale(p.q_up, layer), ts_gate = matrix_scale(p.q_gate, layer);
             for (int i = 0; i < n; ++i) {
-                const int b = __ldg(ins + 3 + i);
+                const int b = ins[3 + i];
                 const float up = round_bf16(collect_block(p, s, st, lane, op, slot) * ts_up);
                 const float gate = round_bf16(collect_block(p, s, st, lane, op, slot) * ts_gate);
                 float act = gate / (1.0f + expf(-gate));
@@ -1588,7 +1613,8 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             }
             // per 2048-column slice of the product (what one down-projection
             // instruction reads), then the reference interpreter's single counter
-            const int my_slice = lane < n ? (__ldg(ins + 3 + lane) * kBlockRows) / p.down_width : -1;
+            const int listed = ins[(3 + lane) & 31];  // lane i reads list entry i (every lane takes part in the shuffle)
+            const int my_slice = lane < n ? (listed * kBlockRows) / p.down_width : -1;
             __syncwarp();
             for (int sl = 0; sl < p.down_slices; ++sl) {
                 const int cnt = __popc(__ballot_sync(0xffffffffu, my_slice == sl));
@@ -1602,7 +1628,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             // tagged cell; folding the slices into the residual stream is a separate
             // step (fold_down_blocks), run once this SM has parked all of its slices
             // of the layer.
-            const int layer = __ldg(ins + 1), b0 = __ldg(ins + 2), b1 = __ldg(ins + 3), red = __ldg(ins + 4);
+            const int layer = ins[1], b0 = ins[2], b1 = ins[3], red = ins[4];
             if (p.down_local) {
                 // This SM holds every column slice of rows [b0*16, b1*16) as consecutive
                 // instructions in slice order, so the interpreter's sequential
@@ -1658,7 +1684,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
                                    p.t_hidden + (size_t)layer * (p.hidden / 2), op, slot);
                 publish(p, s, lane, counter(p, layer, 5, 0), S * nb);  // what the S instructions add together
                 slot += S - 1;
-                next_op = opcode_at(p, slot + 1);
+                next_ins = fetch_instruction(p, slot + 1, lane);
                 if (lane == 0) stamp(p, slot, kEvLastStore, t_start);
                 continue;
             }
@@ -1669,7 +1695,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             }
             if (lane == 0) stamp(p, slot, 55, t_start);  // own slices parked
             if (p.down_owner_last) {
-                fold_down_blocks(p, s, lane, tag, ins, slot, t_start);
+                fold_down_blocks(p, s, lane, tag, instruction_at(p, slot), slot, t_start);
             } else {
                 if (run_start < 0 || run_layer != layer) { run_start = slot; run_layer = layer; }
                 int nxt = slot + 1;
@@ -1688,7 +1714,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
             break;
         }
         case 7: {
-            const int b0 = __ldg(ins + 1), b1 = __ldg(ins + 2);
+            const int b0 = ins[1], b1 = ins[2];
             unsigned long long best = 0ull;
             const float ts = matrix_scale(p.q_lm, 0);
             for (int b = b0; b < b1; ++b) {
@@ -2004,7 +2030,6 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.spin_cycles = 4000000000ll;
     p.early_shift = 0;
     p.max_inflight = kMaxStages;
-    p.l2_ahead = 0;
     p.o_cols = o_cols;
     p.o_chunks = o_cols >= kChunkCols ? o_cols / kChunkCols : 1;
     p.o_width = o_cols >= kChunkCols ? kChunkCols : o_cols;
@@ -2261,10 +2286,6 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     case MK_OPT_DOWN_FOLD_LOCAL:
         h->fold_spread_forced = value == 0;
         h->params.down_local = h->fold_local_detected && !h->fold_last_forced && !h->fold_spread_forced;
-        return 0;
-    case MK_OPT_L2_AHEAD_TILES:
-        if (value < 0 || value > 64) return fail(MK_ERR_BAD_ARGUMENT, "L2 look-ahead must be 0..64 tiles");
-        h->params.l2_ahead = (int)value;
         return 0;
     case MK_OPT_EARLY_POLL_SHIFT:
         if (value < 0 || value > 31) return fail(MK_ERR_BAD_ARGUMENT, "early-poll shift must be 0..31");

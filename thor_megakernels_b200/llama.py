@@ -53,6 +53,28 @@ class LlamaConfig:
     )
 
 
+def config_from_pretrained(path) -> LlamaConfig:
+    """``config.json`` of a Hugging Face Llama checkpoint directory -> ``LlamaConfig``
+    (stands in for ``transformers.LlamaConfig.from_pretrained``, reference
+    llama.py:596)."""
+    import json
+    from pathlib import Path
+
+    raw = json.loads((Path(path) / "config.json").read_text())
+    heads = raw["num_attention_heads"]
+    scaling = raw.get("rope_scaling")
+    if scaling is not None:
+        scaling = dict(scaling)
+        scaling.setdefault("rope_type", scaling.pop("type", "llama3"))
+    return LlamaConfig(
+        hidden_size=raw["hidden_size"], num_hidden_layers=raw["num_hidden_layers"], num_attention_heads=heads,
+        num_key_value_heads=raw.get("num_key_value_heads", heads), head_dim=raw.get("head_dim") or raw["hidden_size"] // heads,
+        intermediate_size=raw["intermediate_size"], vocab_size=raw["vocab_size"], rms_norm_eps=raw.get("rms_norm_eps", 1e-5),
+        rope_theta=raw.get("rope_theta", 500000.0), max_position_embeddings=raw.get("max_position_embeddings", 131072),
+        tie_word_embeddings=raw.get("tie_word_embeddings", False), rope_scaling=scaling,
+    )
+
+
 def llama_1b_config(**overrides) -> LlamaConfig:
     """Llama-3.2-1B architecture."""
     return LlamaConfig(**overrides)
@@ -364,6 +386,103 @@ class LlamaForCausalLM(nn.Module):
         if finalize:
             model.finalize()
         return model
+
+    # -- checkpoints -----------------------------------------------------------
+    @classmethod
+    def from_pretrained(cls, model_path, extra_config: ExtraModelConfig | None = None, device: DeviceType = "cpu",
+                        dtype: torch.dtype = torch.bfloat16) -> "LlamaForCausalLM":
+        """Load a Hugging Face Llama checkpoint directory (``config.json`` +
+        safetensors) - reference llama.py:583-638.  With
+        ``extra_config.tp_size > 1`` the model is built for rank
+        ``extra_config.tp_rank``'s share - query and KV heads and the FFN width
+        divided by ``tp_size`` (reference llama.py:192-207, 308-310) - and only
+        that share of q/k/v/up/gate rows and o/down columns is read from disk
+        (:665-691): the result has the layout ``tp.shard_model`` produces, except
+        that embedding and LM head stay whole as in the reference.  Only local
+        directories are supported (no download)."""
+        import dataclasses
+        from pathlib import Path
+
+        extra = extra_config or ExtraModelConfig()
+        path = Path(model_path)
+        if not path.exists():
+            raise FileNotFoundError(f"{model_path}: only local checkpoint directories can be loaded")
+        cfg = config_from_pretrained(path)
+        if extra.rope_scaling is not None:
+            cfg = dataclasses.replace(cfg, rope_scaling=dict(extra.rope_scaling))
+        whole = cfg
+        if extra.tp_size > 1:
+            for what, n in (("attention heads", cfg.num_attention_heads), ("KV heads", cfg.num_key_value_heads),
+                            ("intermediate size", cfg.intermediate_size)):
+                if n % extra.tp_size:
+                    raise ValueError(f"{what} ({n}) do not divide over {extra.tp_size} ranks")
+            cfg = dataclasses.replace(cfg, num_attention_heads=cfg.num_attention_heads // extra.tp_size,
+                                      num_key_value_heads=cfg.num_key_value_heads // extra.tp_size,
+                                      intermediate_size=cfg.intermediate_size // extra.tp_size)
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(dtype)
+        try:
+            with torch.device("meta"):
+                model = cls(cfg, extra)
+        finally:
+            torch.set_default_dtype(prev)
+        model.device, model.dtype = torch.device(device), dtype
+        model.whole_config = whole
+        model.load_from_safetensors(path)
+        # rotary tables are buffers built on the meta device: rebuild them for real
+        n = extra.max_len_override or cfg.max_position_embeddings
+        cos, sin = rope_tables(cfg, max(n, 1))
+        model.model.rope_cos, model.model.rope_sin = cos.to(device), sin.to(device)
+        model.finalize()
+        return model
+
+    def make_name_to_hf_name(self) -> dict[str, str]:
+        """This container's parameter names -> names in a Hugging Face Llama
+        checkpoint (reference llama.py:640-663)."""
+        names = {k: k for k in self.state_dict().keys()}
+        for i in range(self.config.num_hidden_layers):
+            names[f"model.layers.{i}.self_attn.input_layernorm.weight"] = f"model.layers.{i}.input_layernorm.weight"
+            names[f"model.layers.{i}.mlp.input_layernorm.weight"] = f"model.layers.{i}.post_attention_layernorm.weight"
+        names["model.embed_tokens.embed_tokens.weight"] = "model.embed_tokens.weight"
+        names["lm_head.input_norm.weight"] = "model.norm.weight"
+        names["lm_head.lm_head.weight"] = "model.embed_tokens.weight" if self.config.tie_word_embeddings else "lm_head.weight"
+        return names
+
+    def make_tp_map(self) -> dict[str, int]:
+        """Hugging Face parameter name -> dimension it is split on across
+        tensor-parallel ranks; parameters not listed are replicated (reference
+        llama.py:665-691, keyed here by checkpoint name because that is what the
+        loader sees)."""
+        by_rows = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "up_proj.weight", "gate_proj.weight")
+        by_cols = ("o_proj.weight", "down_proj.weight")
+        out = {}
+        for hf_name in self.make_name_to_hf_name().values():
+            if hf_name.endswith(by_rows):
+                out[hf_name] = 0
+            elif hf_name.endswith(by_cols):
+                out[hf_name] = 1
+        return out
+
+    def load_from_safetensors(self, model_path):
+        """reference llama.py:693-711"""
+        from .utils import load_safetensors_repo
+
+        names = self.make_name_to_hf_name()
+        hf = load_safetensors_repo(model_path, include_parameters=set(names.values()), device=self.device,
+                                   tp_rank=self.extra_config.tp_rank, tp_size=self.extra_config.tp_size,
+                                   tp_map=self.make_tp_map())
+        state = {k: hf[v].to(self.dtype) for k, v in names.items()}
+        self.load_state_dict(state, assign=True, strict=True)
+
+    def to_hf_state_dict(self) -> dict[str, Tensor]:
+        """Hugging Face-named tensors of a model that has NOT been finalised (row
+        order as in a checkpoint); what ``save_file`` needs to write a checkpoint
+        this class can load back."""
+        state = self.state_dict()
+        out = {}
+        for name, hf_name in self.make_name_to_hf_name().items():
+            out.setdefault(hf_name, state[name].detach().contiguous())
+        return out
 
     def finalize(self):
         """What the reference's ``from_pretrained`` does after loading
