@@ -27,8 +27,9 @@ and whole and the agreement goes into ``tp_parity``.  At every N the line also
 carries ``llama8b_tp``: the Llama-3.1-8B architecture at batch 1 with 8192
 cached positions on the same N GPUs, bf16 and NVFP4 weight-only.
 
-Other workloads: ``--workload llama8b-tp`` / ``llama1b-tp`` run only the split
-decode; ``gemv`` the single-operator GEMV (bf16 and NVFP4 weights, batch 1 and
+Other workloads: ``--workload llama1b-batched`` decodes 16 / 64 / 128 sequences
+with independent cache lengths per step (tcgen05 linears); ``llama8b-tp`` /
+``llama1b-tp`` run only the split decode; ``gemv`` the single-operator GEMV (bf16 and NVFP4 weights, batch 1 and
 4); ``llama1b-nvfp4-4k`` the NVFP4 weight-only megakernel against bf16 weights
 at 4096 cached positions; ``timeline`` one step with per-instruction clock
 stamps, summarised per opcode; ``profile-step`` a few bare steps for a profiler
@@ -794,6 +795,94 @@ def build_step_model(args, device):
     return model, sched, dict(MODEL)
 
 
+def run_batched(args, rank, world, local):
+    """Batched decode (config 3): the 1B architecture, 16 / 64 / 128 sequences
+    with independent cache lengths drawn uniformly from [512, 4096] (seed 3),
+    128 greedy steps per measurement, linears on the tcgen05 tensor cores.  A
+    step is captured once in a CUDA graph (about 165 launches) and replayed; the
+    positions advance on the device between replays."""
+    if rank != 0:
+        return
+    from thor_megakernels_b200.batched import BatchedDecoder
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    cfg = dict(MODEL)
+    steps_per_run, max_ctx = 128, 4096
+    peak, peak_src = measured_hbm_peak()
+    results = []
+    for batch in (16, 64, 128):
+        extra = ExtraModelConfig(interleave_rope=True, max_len_override=max_ctx + steps_per_run + 8, max_batch_size=batch)
+        model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=0, device=device, generate_on=device)
+        gen = torch.Generator().manual_seed(3)
+        lengths = torch.randint(512, max_ctx + 1, (batch,), generator=gen)
+        dgen = torch.Generator(device=device).manual_seed(3)
+        for cache in model.stacked_kv_cache:
+            for b in range(batch):
+                n = int(lengths[b])
+                cache[:, b, :n] = torch.randn(cache[:, b, :n].shape, generator=dgen, device=device).bfloat16()
+        dec = BatchedDecoder(model, batch)
+        tokens = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).int().to(device)
+        start_pos = lengths.int().to(device)
+        pos = start_pos.clone()
+        out = torch.zeros(batch, dtype=torch.int32, device=device)
+        stream = torch.cuda.Stream(device)
+        with torch.cuda.stream(stream):
+            dec.step(tokens, pos, out)   # outside capture once
+            stream.synchronize()
+            dec.status()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                dec.step(tokens, pos, out)
+                tokens.copy_(out)
+                pos.add_(1)
+
+            def run():
+                pos.copy_(start_pos)
+                for _ in range(steps_per_run):
+                    graph.replay()
+
+            for _ in range(max(args.warmup, 3) if args.steps > 2 else 1):
+                run()
+            stream.synchronize()
+            dec.status()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(1, min(args.steps, 5))
+            start.record(stream)
+            for _ in range(reps):
+                run()
+            end.record(stream)
+            stream.synchronize()
+        dec.status()
+        ms_per_step = start.elapsed_time(end) / (reps * steps_per_run)
+        kv = kv_bytes_per_position(cfg)
+        kv_bytes = float(sum(kv * (int(n) + steps_per_run / 2 + 1) for n in lengths))   # mean over the run's positions
+        weight_bytes = linear_weight_bytes(cfg)
+        gbs = (weight_bytes + kv_bytes) / (ms_per_step * 1e-3) / 1e9
+        flops = 2.0 * batch * (weight_bytes / 2)
+        results.append({"batch": batch, "ms_per_step": ms_per_step, "tokens_per_s": batch / (ms_per_step * 1e-3),
+                        "algorithmic_bytes_per_step": weight_bytes + kv_bytes, "kv_share": kv_bytes / (weight_bytes + kv_bytes),
+                        "GB/s": gbs, "frac_of_measured_peak": gbs / peak, "linear_TFLOPs": flops / (ms_per_step * 1e-3) / 1e12,
+                        "mean_cache_length": float(lengths.float().mean())})
+        dec.close()
+        del dec, model
+        torch.cuda.empty_cache()
+    best = max(results, key=lambda r: r["tokens_per_s"])
+    line = {"metric": "decode_tokens_per_s", "value": best["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama-3.2-1b-arch bf16 batched greedy decode, 16/64/128 sequences, cache lengths uniform in "
+                                   "[512, 4096] (seed 3), 128 steps per run; value = best batch size",
+                       "step": "one decode step for the whole batch = one CUDA graph replay (tcgen05 linears + batched attention)",
+                       "l2": "inputs larger than L2 (weights 2.47 GB + KV 0.6-9.7 GB per step)"},
+            "roofline": {"bound": "hbm", "achieved": best["GB/s"], "peak": peak, "unit": "GB/s", "frac": best["GB/s"] / peak,
+                         "traffic": None, "peak_source": peak_src},
+            "cases": results, "gpu_launches": None, "cpu_baseline": None}
+    print(json.dumps(line), flush=True)
+
+
 def run_timeline(args, rank, world, local):
     """One decode step with per-instruction clock stamps; prints, per opcode of a
     middle layer, when its instructions had their input, how long they streamed
@@ -926,7 +1015,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-8b", action="store_true", help="leave out the nested Llama-3.1-8B record")
     ap.add_argument("--workload", default="llama1b",
-                    choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k", "timeline", "profile-step"],
+                    choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k", "llama1b-batched", "timeline", "profile-step"],
                     help="llama1b: the headline workload (split over the GPUs when N > 1); *-tp: only the split decode")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"], help="weight format (tp, timeline, profile-step)")
     ap.add_argument("--schedule", default="b200", choices=["b200", "rr", "zz", "wave", "dag"],
@@ -950,6 +1039,8 @@ def main():
             run_gemv(args, rank, world, local)
         elif args.workload == "llama1b-nvfp4-4k":
             run_long_context(args, rank, world, local)
+        elif args.workload == "llama1b-batched":
+            run_batched(args, rank, world, local)
         elif args.workload == "timeline":
             run_timeline(args, rank, world, local)
         elif args.workload == "profile-step":

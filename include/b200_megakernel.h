@@ -271,10 +271,13 @@ int mk_nvfp4_quantize(const void *input_bf16, void *packed, void *scales, float 
  * The call allocates nothing (the reference's per-call entry points borrow all
  * memory from the caller).  When k > 2048 the K dimension is split over CTAs and
  * the fp32 partial sums go through `workspace`: device memory of at least
- * mk_gemv_workspace_bytes(m, k) bytes, 256-byte aligned, owned by the caller.
- * Calls that may overlap in time (different streams) need different
- * workspaces; calls on one stream can share one.  workspace may be NULL when
- * mk_gemv_workspace_bytes returns 0.
+ * mk_gemv_workspace_bytes(m, k) bytes, 256-byte aligned, owned by the caller
+ * and zeroed by the caller ONCE before its first use (every call leaves it
+ * zeroed again).  Calls that may overlap in time (different streams) need
+ * different workspaces; calls on one stream can share one.  workspace may be
+ * NULL when mk_gemv_workspace_bytes returns 0.  The kernel is launched with
+ * programmatic stream serialization: consecutive calls on a stream overlap
+ * the end of one with the weight fetch of the next.
  *
  * NVFP4 weights: the activations are converted from bf16 to f16 for the tensor
  * cores (code x block scale is exact in f16).  Values beyond +-65504 are clamped
@@ -359,7 +362,15 @@ int mk_linear_batched_nvfp4(const void *w_packed, const void *w_scales_native, f
  * container serves both.  Linears run on the tcgen05 tensor cores
  * (mk_linear_batched); what lies between them are small stream-ordered kernels.
  *
- * mk_batched_create: `desc` as for mk_create with bf16 weights and embed_w;
+ * mk_batched_create: `desc` as for mk_create with embed_w and either bf16
+ *   weights or MK_WEIGHTS_NVFP4 tables (packed codes + canonical scales as
+ *   mk_nvfp4_quantize writes them; the handle keeps its own copy of the scales
+ *   in the tensor core's native layout).  With NVFP4 weights the step is W4A4
+ *   as in the reference's native FP4 path (experimental/native_fp4_vm/model.cu:
+ *   102-200, include/ops/nvfp4_linear.cuh:174-237): before every linear its
+ *   bf16 input panel is quantised to NVFP4 (tensor scale set by
+ *   mk_batched_set_activation_scale, default 1) and the linear runs as
+ *   tcgen05 block-scaled MMA; the SiLU product is rounded once.
  *   k_cache / v_cache [L, kv_batch >= max_batch, kv_max_len, Hkv, D];
  *   hidden_states [max_batch, hidden] and logits [max_batch, vocab] (bf16) are
  *   the step's residual-stream and logits outputs.  The other activation
@@ -377,6 +388,7 @@ int mk_batched_create(const MkModelDesc *desc, int32_t max_batch, void **handle)
 int mk_step_batched(void *handle, const int32_t *tokens_in, const int32_t *pos_ids, int32_t batch,
                     int32_t *tokens_out, void *stream);
 int mk_batched_status(void *handle, void *stream);
+int mk_batched_set_activation_scale(void *handle, float tensor_scale);
 void mk_batched_destroy(void *handle);
 
 #ifdef __cplusplus

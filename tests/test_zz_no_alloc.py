@@ -28,7 +28,7 @@ def test_two_calls_in_a_row_equal_mk_gemv(packed, m, k):
     gen = torch.Generator(device="cuda").manual_seed(2)
     w = (torch.randn(m, k, device="cuda", generator=gen) * 0.02).bfloat16()
     q = quantize_weight(w) if packed else None
-    workspace = torch.empty(max(256, int(lib.mk_gemv_workspace_bytes(m, k))), dtype=torch.uint8, device="cuda")
+    workspace = torch.zeros(max(256, int(lib.mk_gemv_workspace_bytes(m, k))), dtype=torch.uint8, device="cuda")
     # one call first: it resolves the fixed array's address on this device (no allocation, but a driver look-up)
     x = torch.randn(1, k, device="cuda", generator=gen).bfloat16()
     assert _call(lib.mk_gemv_static, w, q, x, torch.empty((1, m), dtype=torch.bfloat16, device="cuda")) == 0
@@ -59,7 +59,7 @@ def test_largest_supported_split_matches_mk_gemv():
     gen = torch.Generator(device="cuda").manual_seed(4)
     w = (torch.randn(m, k, device="cuda", generator=gen) * 0.02).bfloat16()
     x = torch.randn(1, k, device="cuda", generator=gen).bfloat16()
-    workspace = torch.empty(int(lib.mk_gemv_workspace_bytes(m, k)), dtype=torch.uint8, device="cuda")
+    workspace = torch.zeros(int(lib.mk_gemv_workspace_bytes(m, k)), dtype=torch.uint8, device="cuda")
     want = torch.empty((1, m), dtype=torch.bfloat16, device="cuda")
     got = torch.empty((1, m), dtype=torch.bfloat16, device="cuda")
     assert _call(lib.mk_gemv, w, None, x, want, workspace) == 0, lib.mk_last_error()

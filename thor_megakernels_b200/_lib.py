@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = [
     "mk_linear_batched", "mk_linear_batched_splits",
     "mk_nvfp4_native_scale_bytes", "mk_nvfp4_quantize_native", "mk_linear_batched_nvfp4",
     "mk_batched_create", "mk_step_batched", "mk_batched_status", "mk_batched_destroy",
+    "mk_batched_set_activation_scale",
 ]
 
 
@@ -124,6 +125,7 @@ def load() -> C.CDLL:
     lib.mk_batched_create.argtypes = [C.POINTER(MkModelDesc), i32, C.POINTER(vp)]
     lib.mk_step_batched.argtypes = [vp, vp, vp, i32, vp, vp]
     lib.mk_batched_status.argtypes = [vp, vp]
+    lib.mk_batched_set_activation_scale.argtypes = [vp, f32]
     lib.mk_batched_destroy.argtypes = [vp]
     lib.mk_batched_destroy.restype = None
     lib.mk_tp_init.argtypes = [vp, i32, i32, i32, vp]

@@ -123,7 +123,11 @@ class BatchedDecoder:
     cache slot ``b``.  After ``step`` the residual stream is in ``hidden``
     ``[batch, hidden]`` and the logits in ``logits`` ``[batch, vocab]``."""
 
-    def __init__(self, model, max_batch: int):
+    def __init__(self, model, max_batch: int, quantized: dict | None = None, activation_scale: float = 1.0):
+        """``quantized``: result of ``nvfp4.quantize_model(model)`` to run every
+        linear as NVFP4 x NVFP4 on the block-scaled tensor-core path (the
+        activations are quantised on the fly with ``activation_scale`` as their
+        tensor scale); default: bf16 weights."""
         import ctypes as C
         import math
 
@@ -141,13 +145,26 @@ class BatchedDecoder:
         head = model.lm_head.lm_head.weight.data
         self._keep = [sp, k, v, embed, head, model.model.rope_cos, model.model.rope_sin, model.lm_head.input_norm.weight]
         d = _lib.MkModelDesc()
-        d.abi_version, d.weight_format = _lib.MK_ABI_VERSION, _lib.MK_WEIGHTS_BF16
+        d.abi_version = _lib.MK_ABI_VERSION
+        d.weight_format = _lib.MK_WEIGHTS_BF16 if quantized is None else _lib.MK_WEIGHTS_NVFP4
         d.hidden_size, d.num_layers = cfg.hidden_size, cfg.num_hidden_layers
         d.num_q_heads, d.num_kv_heads, d.head_dim = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         d.intermediate_size, d.vocab_size = cfg.intermediate_size, cfg.vocab_size
         d.attn_scale, d.rms_norm_eps = 1 / math.sqrt(cfg.head_dim), float(cfg.rms_norm_eps)
-        d.qkv_w, d.o_w, d.up_w = sp.qkv_proj.data_ptr(), sp.o_proj.data_ptr(), sp.up_proj.data_ptr()
-        d.gate_w, d.down_w, d.lm_head_w = sp.gate_proj.data_ptr(), sp.down_proj.data_ptr(), head.data_ptr()
+        if quantized is None:
+            d.qkv_w, d.o_w, d.up_w = sp.qkv_proj.data_ptr(), sp.o_proj.data_ptr(), sp.up_proj.data_ptr()
+            d.gate_w, d.down_w, d.lm_head_w = sp.gate_proj.data_ptr(), sp.down_proj.data_ptr(), head.data_ptr()
+        else:
+            self._tables = {}
+            for key, field in (("qkv", "qkv_q"), ("o", "o_q"), ("up", "up_q"), ("gate", "gate_q"), ("down", "down_q"),
+                               ("lm_head", "lm_head_q")):
+                mats = quantized[key] if key != "lm_head" else [quantized[key]]
+                table = (_lib.MkNvfp4Matrix * len(mats))()
+                for i, m in enumerate(mats):
+                    table[i].packed, table[i].scales = m.packed.data_ptr(), m.scales.data_ptr()
+                    table[i].tensor_scale = float(m.tensor_scale)
+                self._tables[key] = (table, mats)
+                setattr(d, field, table)
         d.attn_norm_w, d.mlp_norm_w = sp.attn_ln_weight.data_ptr(), sp.mlp_ln_weight.data_ptr()
         d.lm_head_norm_w, d.embed_w = model.lm_head.input_norm.weight.data_ptr(), embed.data_ptr()
         d.k_cache, d.v_cache, d.kv_batch, d.kv_max_len = k.data_ptr(), v.data_ptr(), k.shape[1], k.shape[2]
@@ -159,6 +176,8 @@ class BatchedDecoder:
         self.handle = C.c_void_p()
         with torch.cuda.device(self.device):
             _lib.check(self.lib.mk_batched_create(C.byref(d), max_batch, C.byref(self.handle)))
+            if quantized is not None:
+                _lib.check(self.lib.mk_batched_set_activation_scale(self.handle, float(activation_scale)))
 
     def step(self, tokens: torch.Tensor, pos_ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """``tokens`` and ``pos_ids``: int32 CUDA vectors of the same length

@@ -54,7 +54,13 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_mma_kernel(
     if (row_h >= m) row_h = m - 1;
     const int xcol = g < batch ? g : batch - 1;        // B-operand column g; extra columns repeat the last vector
 
+    // Programmatic dependent launch: the next kernel in the stream may start as soon as
+    // every CTA of this one has got here, and this kernel reads its weights (which no
+    // earlier kernel produces) before it waits for its predecessor.  Activations,
+    // outputs and the split-K scratch are touched only after the wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!active) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (active) {
         if constexpr (PACKED) {
             uint4 cg[2], ch[2];
@@ -64,6 +70,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_mma_kernel(
             ch[0] = __ldg(ph); ch[1] = __ldg(ph + 1);
             const uint32_t sg = __ldg(reinterpret_cast<const uint32_t *>(scales + ((size_t)row_g * k + col0) / 16 + t * 4));
             const uint32_t sh = __ldg(reinterpret_cast<const uint32_t *>(scales + ((size_t)row_h * k + col0) / 16 + t * 4));
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t xh[32];
             const uint4 *xs = reinterpret_cast<const uint4 *>(x + (size_t)xcol * k + col0 + t * 64);
 #pragma unroll
@@ -82,8 +89,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_mma_kernel(
             for (int j = 0; j < 8; ++j) {
                 a[j] = __ldg(reinterpret_cast<const uint4 *>(wg + j * 32));
                 b[j] = __ldg(reinterpret_cast<const uint4 *>(wh + j * 32));
-                xv[j] = __ldg(reinterpret_cast<const uint4 *>(xs + j * 32));
             }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xv[j] = __ldg(reinterpret_cast<const uint4 *>(xs + j * 32));
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 mma_bf16_16816(acc, a[j].x, b[j].x, a[j].y, b[j].y, xv[j].x, xv[j].y);
@@ -141,6 +150,25 @@ size_t gemv_workspace_bytes(int m, int k) {
     return gemv_ticket_bytes(m) + (size_t)chunks * kGemvMaxBatch * (size_t)m * sizeof(float);
 }
 
+// Launch with the programmatic-stream-serialization attribute, so that back-to-back
+// GEMVs on one stream overlap one kernel's tail and the next one's start.
+template <bool PACKED>
+static cudaError_t launch_overlapped(dim3 grid, dim3 block, cudaStream_t stream, const bf16 *w, const uint8_t *packed,
+                                     const uint8_t *scales, const bf16 *x, bf16 *y, int m, int k, float ts, int batch, int chunks,
+                                     float *partial, int *tickets) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<PACKED>, w, packed, scales, x, y, m, k, ts, batch, chunks, partial, tickets);
+}
+
 cudaError_t launch_gemv_mma(const void *w, const void *packed, const void *scales, const void *x, void *y, int m, int k,
                             float ts, int is_packed, int batch, void *workspace, cudaStream_t stream) {
     const int row_blocks = (m + kGemvRows - 1) / kGemvRows;
@@ -148,20 +176,19 @@ cudaError_t launch_gemv_mma(const void *w, const void *packed, const void *scale
     float *partial = nullptr;
     int *tickets = nullptr;
     if (chunks > 1) {
+        // The tickets count arrivals per row block.  They must be zero when a call starts: the
+        // caller zeroes the workspace once, and the last CTA of every row block puts its ticket
+        // back to zero, so the workspace stays ready for the next call.  The partial sums are
+        // written before they are read.
         tickets = reinterpret_cast<int *>(workspace);
         partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) + gemv_ticket_bytes(m));
-        // the tickets count arrivals per row block and must start at zero; the partial sums are written before they are read
-        cudaError_t e = cudaMemsetAsync(tickets, 0, row_blocks * sizeof(int), stream);
-        if (e != cudaSuccess) return e;
     }
     const dim3 grid(row_blocks * chunks), block(kGemvWarps * 32);
     if (is_packed)
-        gemv_mma_kernel<true><<<grid, block, 0, stream>>>(nullptr, (const uint8_t *)packed, (const uint8_t *)scales,
-                                                          (const bf16 *)x, (bf16 *)y, m, k, ts, batch, chunks, partial, tickets);
-    else
-        gemv_mma_kernel<false><<<grid, block, 0, stream>>>((const bf16 *)w, nullptr, nullptr, (const bf16 *)x, (bf16 *)y,
-                                                           m, k, 1.0f, batch, chunks, partial, tickets);
-    return cudaGetLastError();
+        return launch_overlapped<true>(grid, block, stream, nullptr, (const uint8_t *)packed, (const uint8_t *)scales, (const bf16 *)x,
+                                       (bf16 *)y, m, k, ts, batch, chunks, partial, tickets);
+    return launch_overlapped<false>(grid, block, stream, (const bf16 *)w, nullptr, nullptr, (const bf16 *)x, (bf16 *)y, m, k, 1.0f,
+                                    batch, chunks, partial, tickets);
 }
 
 // ---------------------------------------------------------------------------

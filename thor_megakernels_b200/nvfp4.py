@@ -67,7 +67,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)  # zeroed once; calls leave it zeroed
         _workspaces[key] = buf
     return buf
 
