@@ -371,7 +371,7 @@ int mk_linear_batched_nvfp4(const void *w_packed, const void *w_scales_native, f
  *   bf16 input panel is quantised to NVFP4 (tensor scale set by
  *   mk_batched_set_activation_scale, default 1) and the linear runs as
  *   tcgen05 block-scaled MMA; the SiLU product is rounded once.
- *   k_cache / v_cache [L, kv_batch >= max_batch, kv_max_len, Hkv, D];
+ *   k_cache / v_cache [L, kv_batch, kv_max_len, Hkv, D] (mk_step_batched needs kv_batch >= batch);
  *   hidden_states [max_batch, hidden] and logits [max_batch, vocab] (bf16) are
  *   the step's residual-stream and logits outputs.  The other activation
  *   pointers, barriers and counters of `desc` are not used.  Allocates the
@@ -388,8 +388,92 @@ int mk_batched_create(const MkModelDesc *desc, int32_t max_batch, void **handle)
 int mk_step_batched(void *handle, const int32_t *tokens_in, const int32_t *pos_ids, int32_t batch,
                     int32_t *tokens_out, void *stream);
 int mk_batched_status(void *handle, void *stream);
+/*
+ * Prompt processing (prefill) on the device, replacing the PyTorch forward of
+ * megakernels/scripts/generate.py:125-132.  tokens: device int32 [count]; the
+ * prompt occupies positions start_pos .. start_pos+count-1 of cache slot `slot`
+ * (the batch-1 megakernel uses slot 0), processed max_batch tokens per pass with
+ * causal attention.  token_out (optional, device int32[1]) receives the greedy
+ * token after the last prompt position; its logits are row 0 of `logits`, and
+ * hidden_states holds the residual streams of the last pass's tokens.  The cache
+ * only needs the one slot.  Asynchronous on `stream`; allocates nothing.
+ */
+int mk_prefill_batched(void *handle, const int32_t *tokens, int32_t count, int32_t slot, int32_t start_pos,
+                       int32_t *token_out, void *stream);
 int mk_batched_set_activation_scale(void *handle, float tensor_scale);
 void mk_batched_destroy(void *handle);
+
+/*
+ * The reference's batched instruction set (opcodes 1-10,
+ * megakernels/demos/throughput/instructions.py:57-223) on a batched handle.
+ * Replaces the native call of megakernels/demos/throughput/mk.py:7-49 (whose
+ * kernel the reference project does not ship).  Semantics are those of the
+ * reference's interpreter (throughput/python_vm.py:44-465): one pos_id for the
+ * whole batch, half-split rotary embedding (no weight permutation), the down
+ * projection added to the residual stream as one bf16 addend, the residual
+ * stream read from and left in hidden_states, no embedding and no argmax.
+ *
+ * mk_throughput_bind: the caller's activation buffers (bf16, row-major
+ *   [batch_size, width]; widths: hidden for the three rms_* buffers, Hq*D for
+ *   post_ln_rope_q and attn_out, intermediate for silu_out).  batch_size is a
+ *   multiple of 128 and at most the cache's batch; the descriptor's
+ *   hidden_states / logits given to mk_batched_create must hold batch_size rows
+ *   and the handle must have been created with max_batch 128 (sequences are
+ *   processed 128 at a time).  barriers (optional) is the instruction set's
+ *   counter tensor int32 [layers, 10, batch_size, barrier_cols]: after a step it
+ *   holds the final counts of the operators the schedule covers, as the
+ *   reference's interpreter leaves them.
+ * mk_throughput_set_schedule: instructions int32 [workers, queue_len, 32]
+ *   (device) in the reference's wire format.  Copied to the host once and
+ *   checked: every operand in range, and every operator (layer, opcode) either
+ *   absent or present with all of its instructions - operators run whole, in
+ *   opcode order within a layer, whatever their placement in the queues.
+ *   MK_ERR_UNSUPPORTED for a partial operator or opcode 7 without opcode 6.
+ * mk_step_throughput: one step at `pos_id` on `stream`; allocates nothing.
+ */
+typedef struct MkThroughputBuffers {
+    void *rms_rope_intermediates, *rms_gate_intermediates, *rms_lm_head_intermediates;
+    void *post_ln_rope_q, *attn_out, *silu_out;
+    int32_t *barriers;
+    int32_t barrier_cols;
+    int32_t batch_size;
+} MkThroughputBuffers;
+int mk_throughput_bind(void *handle, const MkThroughputBuffers *buffers);
+int mk_throughput_set_schedule(void *handle, const int32_t *instructions, int32_t workers, int32_t queue_len);
+int mk_step_throughput(void *handle, int32_t pos_id, void *stream);
+
+/*
+ * A prepared chain of NVFP4 x NVFP4 linears: the counterpart of the reference's
+ * native-FP4 micro-VM surface, experimental/native_fp4_vm/vm.cu:14-63
+ * (vm_prepare / vm_run / vm_destroy).  Operand i computes
+ *     output[b, :m] = bf16(alpha * sum_k decode(W)[.., k] * decode(X)[b, k])
+ * where decode() is code x block scale (tensor scales are folded into alpha, as
+ * in the reference: alpha = weight tensor scale x input tensor scale).  With
+ * `quantize` != 0 the bf16 `input` [batch, k] is quantised on the fly with
+ * `input_tensor_scale` (the reference's Quantize instruction,
+ * include/ops/nvfp4_linear.cuh:174-237); otherwise x_packed / x_scales_native
+ * hold the panel already (mk_nvfp4_quantize_native).  Operands run in order on
+ * the stream, so output[i] may be input[i + 1] (the reference's `dependent`
+ * mode).  The reference's worker count, no-op padding and quantiser-worker
+ * arguments have no counterpart: each operand's launches fill the GPU.
+ * m % 8 == 0, k % 256 == 0 (the reference's rule), batch 1..128 (the
+ * reference's VM is batch 1).  prepare allocates the scratch, run nothing.
+ */
+typedef struct MkFp4ChainOperand {
+    const void *input;            /* bf16 [batch, k]  (quantize != 0) */
+    const void *x_packed;         /* NVFP4 codes [batch, k/2] and ...  (quantize == 0) */
+    const void *x_scales_native;  /* ... block scales in the native layout */
+    void *output;                 /* bf16 [batch, m] */
+    const void *w_packed;         /* [m, k/2] */
+    const void *w_scales_native;  /* native layout, mk_nvfp4_native_scale_bytes(m, k) bytes */
+    int32_t m, k;
+    float input_tensor_scale;
+    float alpha;
+} MkFp4ChainOperand;
+int mk_fp4_chain_prepare(const MkFp4ChainOperand *operands, int32_t length, int32_t batch, int32_t quantize, void **handle);
+int mk_fp4_chain_run(void *handle, void *stream);
+int mk_fp4_chain_status(void *handle, void *stream);
+void mk_fp4_chain_destroy(void *handle);
 
 #ifdef __cplusplus
 }

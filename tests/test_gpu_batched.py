@@ -252,3 +252,59 @@ def test_two_layer_model_nvfp4_weights_and_activations():
     print(f"worst NRMSE over {batch} sequences: hidden {worst_h:.4f}, logits {worst_l:.4f}")
     assert worst_h <= 0.03 and worst_l <= 0.03
     dec.close()
+
+
+@pytest.mark.parametrize("batch", [1, 16])
+def test_fp4_chain_of_dependent_linears(batch):
+    """``mk_fp4_chain_*`` (the counterpart of the reference's vm_prepare / vm_run,
+    experimental/native_fp4_vm/vm.cu:14-63): up projection 2048 -> 8192 whose
+    output feeds a down projection 8192 -> 2048, inputs quantised on the fly.
+    Oracle per operand: numpy quantiser on the operand's actual input, decoded
+    operands, float64 dot products, one bf16 rounding."""
+    import numpy as np
+
+    from oracle import nvfp4 as oracle
+    from thor_megakernels_b200 import batched
+
+    gen = torch.Generator(device="cuda").manual_seed(40 + batch)
+    w1 = (torch.randn(8192, 2048, device="cuda", generator=gen) * 0.02).bfloat16()
+    w2 = (torch.randn(2048, 8192, device="cuda", generator=gen) * 0.02).bfloat16()
+    x = torch.randn(batch, 2048, device="cuda", generator=gen).bfloat16()
+    y1 = torch.zeros(batch, 8192, dtype=torch.bfloat16, device="cuda")
+    y2 = torch.zeros(batch, 2048, dtype=torch.bfloat16, device="cuda")
+    q1, q2 = batched.quantize_native(w1), batched.quantize_native(w2)
+    scales = [float(oracle.tensor_scale_for(x.abs().max().item())), 0.9 / (6 * 448)]
+    chain = batched.Fp4Chain([q1, q2], [x, y1], [y1, y2], scales)
+    for _ in range(2):   # a second run reuses the scratch
+        chain.run()
+    chain.status()
+
+    def expect(qw, inp, ts):
+        dw = oracle.dequantize(qw.packed.cpu().numpy(), qw.canonical_scales().cpu().numpy(), qw.tensor_scale).astype(np.float64)
+        _, _, dx = oracle.quantize(inp.float().cpu().numpy(), np.float32(ts))
+        return torch.from_numpy(dx.astype(np.float64) @ dw.T).float().bfloat16().float()
+
+    want1 = expect(q1, x, scales[0])
+    assert rel_l2(y1.float().cpu(), want1) <= 1e-3
+    assert_close("chain operand 0", y1, want1)
+    want2 = expect(q2, y1, scales[1])     # from the GPU's own y1: the second quantiser sees exactly these values
+    assert rel_l2(y2.float().cpu(), want2) <= 1e-3
+    assert_close("chain operand 1", y2, want2)
+    chain.close()
+
+
+def test_fp4_chain_refuses_unaligned_operands():
+    import ctypes as C
+
+    from thor_megakernels_b200 import _lib
+
+    lib = _lib.load()
+    op = (_lib.MkFp4ChainOperand * 1)()
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    for f in ("input", "output", "w_packed", "w_scales_native"):
+        setattr(op[0], f, buf.data_ptr())
+    op[0].m, op[0].k, op[0].input_tensor_scale, op[0].alpha = 128, 192, 1.0, 1.0   # k not a multiple of 256
+    handle = C.c_void_p()
+    assert lib.mk_fp4_chain_prepare(op, 1, 1, 1, C.byref(handle)) == _lib.MK_ERR_BAD_ARGUMENT
+    op[0].k, op[0].input_tensor_scale = 256, 0.0
+    assert lib.mk_fp4_chain_prepare(op, 1, 1, 1, C.byref(handle)) == _lib.MK_ERR_BAD_ARGUMENT

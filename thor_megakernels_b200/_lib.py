@@ -39,6 +39,8 @@ EXPORTED_SYMBOLS = [
     "mk_nvfp4_native_scale_bytes", "mk_nvfp4_quantize_native", "mk_linear_batched_nvfp4",
     "mk_batched_create", "mk_step_batched", "mk_batched_status", "mk_batched_destroy",
     "mk_batched_set_activation_scale",
+    "mk_fp4_chain_prepare", "mk_fp4_chain_run", "mk_fp4_chain_status", "mk_fp4_chain_destroy",
+    "mk_prefill_batched", "mk_throughput_bind", "mk_throughput_set_schedule", "mk_step_throughput",
 ]
 
 
@@ -66,6 +68,22 @@ class MkModelDesc(C.Structure):
         ("max_partials", C.c_int32), ("silu_out", C.c_void_p), ("logits", C.c_void_p),
         ("barriers", C.c_void_p), ("barrier_rows", C.c_int32), ("barrier_cols", C.c_int32),
         ("skip_attn_reduction", C.c_int32),
+    ]
+
+
+class MkFp4ChainOperand(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("x_packed", C.c_void_p), ("x_scales_native", C.c_void_p), ("output", C.c_void_p),
+        ("w_packed", C.c_void_p), ("w_scales_native", C.c_void_p), ("m", C.c_int32), ("k", C.c_int32),
+        ("input_tensor_scale", C.c_float), ("alpha", C.c_float),
+    ]
+
+
+class MkThroughputBuffers(C.Structure):
+    _fields_ = [
+        ("rms_rope_intermediates", C.c_void_p), ("rms_gate_intermediates", C.c_void_p),
+        ("rms_lm_head_intermediates", C.c_void_p), ("post_ln_rope_q", C.c_void_p), ("attn_out", C.c_void_p),
+        ("silu_out", C.c_void_p), ("barriers", C.c_void_p), ("barrier_cols", C.c_int32), ("batch_size", C.c_int32),
     ]
 
 
@@ -128,12 +146,21 @@ def load() -> C.CDLL:
     lib.mk_batched_set_activation_scale.argtypes = [vp, f32]
     lib.mk_batched_destroy.argtypes = [vp]
     lib.mk_batched_destroy.restype = None
+    lib.mk_fp4_chain_prepare.argtypes = [C.POINTER(MkFp4ChainOperand), i32, i32, i32, C.POINTER(vp)]
+    lib.mk_fp4_chain_run.argtypes = [vp, vp]
+    lib.mk_fp4_chain_status.argtypes = [vp, vp]
+    lib.mk_fp4_chain_destroy.argtypes = [vp]
+    lib.mk_fp4_chain_destroy.restype = None
+    lib.mk_prefill_batched.argtypes = [vp, vp, i32, i32, i32, vp, vp]
+    lib.mk_throughput_bind.argtypes = [vp, C.POINTER(MkThroughputBuffers)]
+    lib.mk_throughput_set_schedule.argtypes = [vp, vp, i32, i32]
+    lib.mk_step_throughput.argtypes = [vp, i32, vp]
     lib.mk_tp_init.argtypes = [vp, i32, i32, i32, vp]
     lib.mk_tp_connect.argtypes = [vp, vp, i32]
     lib.mk_abi_sizeof.argtypes = [i32]
     lib.mk_set_option.argtypes = [vp, i32, C.c_int64]
     for name in EXPORTED_SYMBOLS:
-        if name not in ("mk_last_error", "mk_destroy", "mk_gemv_workspace_bytes", "mk_batched_destroy",
+        if name not in ("mk_last_error", "mk_destroy", "mk_gemv_workspace_bytes", "mk_batched_destroy", "mk_fp4_chain_destroy",
                         "mk_nvfp4_native_scale_bytes"):
             getattr(lib, name).restype = C.c_int
     lib.mk_gemv_workspace_bytes.restype = C.c_int64

@@ -135,8 +135,6 @@ class BatchedDecoder:
         dev = model.device
         sp = model.stacked_params
         k, v = model.stacked_kv_cache
-        if k.shape[1] < max_batch:
-            raise ValueError(f"the model's cache holds {k.shape[1]} sequences, max_batch is {max_batch}")
         self.device = torch.device(dev)
         self.max_batch = max_batch
         self.hidden = torch.zeros((max_batch, cfg.hidden_size), dtype=torch.bfloat16, device=dev)
@@ -171,7 +169,7 @@ class BatchedDecoder:
         d.rope_cos, d.rope_sin = model.model.rope_cos.data_ptr(), model.model.rope_sin.data_ptr()
         d.rope_positions = model.model.rope_cos.shape[0]
         d.hidden_states, d.logits = self.hidden.data_ptr(), self.logits.data_ptr()
-        self.kv_max_len = k.shape[2]
+        self.kv_max_len, self.kv_batch = k.shape[2], k.shape[1]
         self.lib = _lib.load()
         self.handle = C.c_void_p()
         with torch.cuda.device(self.device):
@@ -188,11 +186,27 @@ class BatchedDecoder:
         batch = tokens.numel()
         if pos_ids.numel() != batch:
             raise ValueError("tokens and pos_ids differ in length")
+        if batch > self.kv_batch:
+            raise ValueError(f"the model's cache holds {self.kv_batch} sequences, the batch has {batch}")
         if out is None:
             out = torch.empty(batch, dtype=torch.int32, device=tokens.device)
         with torch.cuda.device(self.device):
             _lib.check(self.lib.mk_step_batched(self.handle, tokens.data_ptr(), pos_ids.data_ptr(), batch, out.data_ptr(),
                                                 _stream(tokens)))
+        return out
+
+    def prefill(self, tokens: torch.Tensor, slot: int = 0, start_pos: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Process a prompt on the device (replaces the PyTorch forward the
+        reference uses for prefill): ``tokens`` (int32 CUDA vector) go to positions
+        ``start_pos ..`` of cache slot ``slot``.  Returns a 1-element int32 tensor
+        with the greedy token that follows the prompt; ``logits[0]`` are its logits."""
+        if tokens.device.type != "cuda" or tokens.dtype != torch.int32 or tokens.ndim != 1 or not tokens.is_contiguous():
+            raise ValueError("tokens must be a contiguous int32 CUDA vector")
+        if out is None:
+            out = torch.empty(1, dtype=torch.int32, device=tokens.device)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_prefill_batched(self.handle, tokens.data_ptr(), tokens.numel(), int(slot), int(start_pos),
+                                                   out.data_ptr(), _stream(tokens)))
         return out
 
     def status(self):
@@ -219,3 +233,156 @@ def check_errors(device=None) -> None:
     if word is not None and int(word.item()) != 0:
         word.zero_()
         raise _lib.MegakernelError(_lib.MK_ERR_DEVICE_WAIT, "a bounded wait inside a batched-decode kernel ran out")
+
+
+class ThroughputExecutor:
+    """The reference's batched instruction set (``demos/throughput``) on the
+    tensor-core batched path: binds a ``Globals``' tensors once, validates an
+    instruction tensor (``set_schedule``) and runs the operators it covers for
+    one decode step at a single ``pos_id`` (``step``).  Semantics follow the
+    reference's interpreter (``megakernels/demos/throughput/python_vm.py``):
+    half-split rotary embedding, residual stream in and out through
+    ``hidden_states``, counters left at their final values in ``barriers``."""
+
+    def __init__(self, *, barriers, qkv_w, attn_norm_w, o_w, mlp_norm_w, up_w, gate_w, down_w, lm_head_norm_w, lm_head_w,
+                 k_cache, v_cache, rope_cos, rope_sin, hidden_states, rms_rope_intermediates, rms_gate_intermediates,
+                 post_ln_rope_q, attn_out, silu_out, rms_lm_head_intermediates, logits, attn_scale, rms_norm_eps, batch_size):
+        import ctypes as C
+
+        tensors = dict(barriers=barriers, qkv_w=qkv_w, attn_norm_w=attn_norm_w, o_w=o_w, mlp_norm_w=mlp_norm_w, up_w=up_w,
+                       gate_w=gate_w, down_w=down_w, lm_head_norm_w=lm_head_norm_w, lm_head_w=lm_head_w, k_cache=k_cache,
+                       v_cache=v_cache, rope_cos=rope_cos, rope_sin=rope_sin, hidden_states=hidden_states,
+                       rms_rope_intermediates=rms_rope_intermediates, rms_gate_intermediates=rms_gate_intermediates,
+                       post_ln_rope_q=post_ln_rope_q, attn_out=attn_out, silu_out=silu_out,
+                       rms_lm_head_intermediates=rms_lm_head_intermediates, logits=logits)
+        for name, t in tensors.items():
+            if t.device.type != "cuda" or not t.is_contiguous():
+                raise RuntimeError(f"{name} must be a contiguous CUDA tensor")
+            want = torch.int32 if name == "barriers" else torch.float32 if name.startswith("rope_") else torch.bfloat16
+            if t.dtype != want:
+                raise RuntimeError(f"{name} must be {want}")
+        self._keep = tensors
+        self.device = hidden_states.device
+        L, qkv_rows, H = qkv_w.shape
+        T, hkv, D = k_cache.shape[-3:]
+        kv_batch = k_cache.shape[0] // L if k_cache.ndim == 4 else k_cache.shape[1]
+        hq = qkv_rows // D - 2 * hkv
+        if barriers.ndim != 4 or barriers.shape[0] != L or barriers.shape[1] != 10 or barriers.shape[2] != batch_size:
+            raise RuntimeError("barriers must be int32 [layers, 10, batch_size, columns]")
+        for name, width in (("hidden_states", H), ("rms_rope_intermediates", H), ("rms_gate_intermediates", H),
+                            ("rms_lm_head_intermediates", H), ("post_ln_rope_q", hq * D), ("attn_out", hq * D),
+                            ("silu_out", up_w.shape[1]), ("logits", lm_head_w.shape[0])):
+            if tuple(tensors[name].shape) != (batch_size, width):
+                raise RuntimeError(f"{name} must be [{batch_size}, {width}], got {tuple(tensors[name].shape)}")
+        d = _lib.MkModelDesc()
+        d.abi_version, d.weight_format = _lib.MK_ABI_VERSION, _lib.MK_WEIGHTS_BF16
+        d.hidden_size, d.num_layers, d.num_q_heads, d.num_kv_heads, d.head_dim = H, L, hq, hkv, D
+        d.intermediate_size, d.vocab_size = up_w.shape[1], lm_head_w.shape[0]
+        d.attn_scale, d.rms_norm_eps = float(attn_scale), float(rms_norm_eps)
+        d.qkv_w, d.o_w, d.up_w, d.gate_w = qkv_w.data_ptr(), o_w.data_ptr(), up_w.data_ptr(), gate_w.data_ptr()
+        d.down_w, d.lm_head_w = down_w.data_ptr(), lm_head_w.data_ptr()
+        d.attn_norm_w, d.mlp_norm_w, d.lm_head_norm_w = attn_norm_w.data_ptr(), mlp_norm_w.data_ptr(), lm_head_norm_w.data_ptr()
+        d.embed_w = lm_head_w.data_ptr()  # required by the descriptor, never read: the set starts from hidden_states
+        d.k_cache, d.v_cache, d.kv_batch, d.kv_max_len = k_cache.data_ptr(), v_cache.data_ptr(), kv_batch, T
+        d.rope_cos, d.rope_sin, d.rope_positions = rope_cos.data_ptr(), rope_sin.data_ptr(), rope_cos.shape[0]
+        d.hidden_states, d.logits = hidden_states.data_ptr(), logits.data_ptr()
+        b = _lib.MkThroughputBuffers()
+        b.rms_rope_intermediates, b.rms_gate_intermediates = rms_rope_intermediates.data_ptr(), rms_gate_intermediates.data_ptr()
+        b.rms_lm_head_intermediates, b.post_ln_rope_q = rms_lm_head_intermediates.data_ptr(), post_ln_rope_q.data_ptr()
+        b.attn_out, b.silu_out, b.barriers = attn_out.data_ptr(), silu_out.data_ptr(), barriers.data_ptr()
+        b.barrier_cols, b.batch_size = barriers.shape[3], batch_size
+        self.lib = _lib.load()
+        self.handle = C.c_void_p()
+        self._schedule_key = None
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_batched_create(C.byref(d), 128, C.byref(self.handle)))
+            try:
+                _lib.check(self.lib.mk_throughput_bind(self.handle, C.byref(b)))
+            except Exception:
+                self.close()
+                raise
+
+    def set_schedule(self, instructions: torch.Tensor) -> None:
+        if instructions.device != self.device or instructions.dtype != torch.int32 or instructions.ndim != 3 \
+                or instructions.shape[2] != 32 or not instructions.is_contiguous():
+            raise RuntimeError("instructions must be a contiguous int32 [workers, queue_len, 32] tensor on the model's device")
+        key = (instructions.data_ptr(), tuple(instructions.shape), instructions._version)
+        if key == self._schedule_key:
+            return
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_throughput_set_schedule(self.handle, instructions.data_ptr(), instructions.shape[0],
+                                                           instructions.shape[1]))
+        self._schedule_key = key
+
+    def step(self, pos_id: int, stream=None) -> None:
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_step_throughput(self.handle, int(pos_id), st.cuda_stream))
+
+    def status(self) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_batched_status(self.handle, torch.cuda.current_stream(self.device).cuda_stream))
+
+    def close(self) -> None:
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            self.lib.mk_batched_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Fp4Chain:
+    """A prepared chain of NVFP4 x NVFP4 linears (``mk_fp4_chain_*``), the
+    counterpart of the reference's ``vm_prepare`` / ``vm_run`` / ``vm_destroy``
+    (``experimental/native_fp4_vm/vm.cu:14-63``).
+
+    ``weights``: list of ``Nvfp4Native``; ``inputs`` / ``outputs``: bf16 CUDA
+    tensors ``[batch, k_i]`` / ``[batch, m_i]`` (``outputs[i] is inputs[i + 1]``
+    makes the chain dependent); ``input_scales``: tensor scale of each input's
+    on-the-fly quantisation."""
+
+    def __init__(self, weights, inputs, outputs, input_scales):
+        import ctypes as C
+
+        if not (len(weights) == len(inputs) == len(outputs) == len(input_scales)) or not weights:
+            raise ValueError("weights, inputs, outputs and input_scales must be non-empty lists of one length")
+        batch = inputs[0].shape[0]
+        ops = (_lib.MkFp4ChainOperand * len(weights))()
+        for i, (w, x, y, ts) in enumerate(zip(weights, inputs, outputs, input_scales)):
+            for name, t, width in (("input", x, w.k), ("output", y, w.rows)):
+                if t.device.type != "cuda" or t.dtype != torch.bfloat16 or not t.is_contiguous() or tuple(t.shape) != (batch, width):
+                    raise ValueError(f"{name} {i} must be a contiguous bf16 CUDA tensor [{batch}, {width}]")
+            ops[i].input, ops[i].output = x.data_ptr(), y.data_ptr()
+            ops[i].w_packed, ops[i].w_scales_native = w.packed.data_ptr(), w.scales.data_ptr()
+            ops[i].m, ops[i].k = w.rows, w.k
+            ops[i].input_tensor_scale, ops[i].alpha = float(ts), float(w.tensor_scale) * float(ts)
+        self._keep = (weights, inputs, outputs)
+        self.device = inputs[0].device
+        self.lib = _lib.load()
+        self.handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_fp4_chain_prepare(ops, len(weights), batch, 1, C.byref(self.handle)))
+
+    def run(self, stream=None) -> None:
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_fp4_chain_run(self.handle, st.cuda_stream))
+
+    def status(self) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.mk_fp4_chain_status(self.handle, torch.cuda.current_stream(self.device).cuda_stream))
+
+    def close(self) -> None:
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            self.lib.mk_fp4_chain_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -13,7 +13,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIBRARY = PACKAGE_DIR / "libb200mk.so"
-SOURCES = ["megakernel.cu", "nvfp4.cu", "gemv.cu", "linear_batched.cu", "batched_ops.cu", "batched_step.cu"]
+SOURCES = ["megakernel.cu", "nvfp4.cu", "gemv.cu", "linear_batched.cu", "batched_ops.cu", "batched_step.cu", "fp4_chain.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

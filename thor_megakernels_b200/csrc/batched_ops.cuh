@@ -23,11 +23,15 @@ cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int
 cudaError_t launch_residual_norm(bf16 *hidden, const bo::LinOut &lin, int add, const bf16 *weight, bf16 *normed, int batch,
                                  int hidden_size, float eps, cudaStream_t st);
 cudaError_t launch_rope_append(const bo::LinOut &qkv, const int *pos_ids, const float *rope_cos, const float *rope_sin, bf16 *q_out,
-                               bf16 *k_cache, bf16 *v_cache, int layer, int batch, int kv_len, int hq, int hkv, int hd,
-                               cudaStream_t st);
+                               bf16 *k_cache, bf16 *v_cache, int layer, int rows, int cache_batch, int kv_len, int hq, int hkv,
+                               int hd, int half_split, int slot_fixed, cudaStream_t st);
+cudaError_t launch_fill_int(int *dst, int value, int step, int n, cudaStream_t st);
+cudaError_t launch_barrier_fill(int *barriers, const int *covered, int layers, int batch, int cols, int batch_blocks, int hq,
+                                int hkv, int out_blocks, int inter_blocks, cudaStream_t st);
+int attention_batched_splits(int batch, int hkv, int sms, int max_splits);
 cudaError_t launch_attention_batched(const bf16 *q, const bf16 *k_cache, const bf16 *v_cache, const int *pos_ids, bf16 *out,
-                                     int layer, int batch, int kv_len, int hq, int hkv, int hd, float attn_scale,
-                                     cudaStream_t st);
+                                     float *partial, int splits, int layer, int batch, int cache_batch, int kv_len, int hq, int hkv,
+                                     int hd, float attn_scale, int slot_fixed, cudaStream_t st);
 cudaError_t launch_silu_mul(const bo::LinOut &up, const bo::LinOut &gate, bf16 *act, int batch, int inter, int round_silu,
                             cudaStream_t st);
 cudaError_t launch_argmax(const bf16 *logits, int *tokens, int batch, int vocab, cudaStream_t st);

@@ -23,6 +23,7 @@
 
 #include <algorithm>
 #include <new>
+#include <vector>
 
 #include "../../include/b200_megakernel.h"
 #include "batched_ops.cuh"
@@ -80,7 +81,14 @@ struct BatchedHandle {
     bf16 *normed = nullptr, *q = nullptr, *attn = nullptr, *act = nullptr;
     bf16 *qkv_y = nullptr, *up_y = nullptr, *gate_y = nullptr;
     float *part_a = nullptr, *part_b = nullptr;  // split-K partial sums (two buffers: up and gate are alive together)
+    float *attn_partial = nullptr;               // attention split states [batch, Hq, kMaxAttnSplits, D + 2]
     int *error_word = nullptr;
+    // batched instruction set (mk_throughput_*)
+    MkThroughputBuffers tp = {};
+    bool tp_bound = false, plan_ready = false;
+    int covered[256] = {};        // per layer: bit (opcode - 1) set when the schedule holds that operator
+    int *covered_dev = nullptr;   // device copy, for the counter fill
+    int *pos_uniform = nullptr;   // [128] the step's position, one per sequence of a block
 };
 
 int fail_msg(int code, const char *text) {
@@ -89,6 +97,8 @@ int fail_msg(int code, const char *text) {
 }
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+constexpr int kMaxAttnSplits = 16;
 
 }  // namespace
 }  // namespace mk
@@ -102,8 +112,8 @@ extern "C" int mk_batched_create(const MkModelDesc *d, int32_t max_batch, void *
     const bool fp4 = d->weight_format == MK_WEIGHTS_NVFP4;
     if (!fp4 && d->weight_format != MK_WEIGHTS_BF16)
         return fail_msg(MK_ERR_UNSUPPORTED, "mk_batched_create: unknown weight format");
-    if (max_batch < 1 || max_batch > 128 || d->kv_batch < max_batch)
-        return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_batched_create: max_batch must be 1..128 and the cache must hold that many sequences");
+    if (max_batch < 1 || max_batch > 128 || d->kv_batch < 1)
+        return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_batched_create: max_batch must be 1..128");
     const int H = d->hidden_size, D = d->head_dim;
     if (H <= 0 || H % 64 || d->intermediate_size % 64 || (D != 64 && D != 128) || d->num_q_heads != 4 * d->num_kv_heads ||
         d->num_q_heads * D % 64)
@@ -172,6 +182,8 @@ extern "C" int mk_batched_create(const MkModelDesc *d, int32_t max_batch, void *
     const size_t o_normed = take(B * H * 2), o_q = take(B * qd * 2), o_attn = take(B * qd * 2), o_act = take(B * inter * 2);
     const size_t o_qkv = take(B * h->qkv_rows * 2), o_up = take(B * inter * 2), o_gate = take(B * inter * 2);
     const size_t o_pa = take(B * part_a * 4), o_pb = take(B * part_b * 4), o_err = take(256);
+    const size_t o_ap = take(B * d->num_q_heads * kMaxAttnSplits * (D + 2) * 4);
+    const size_t o_cov = take(256 * sizeof(int)), o_pos = take(128 * sizeof(int));
     const int max_k = std::max(std::max(H, qd), inter);
     const size_t o_xp = take(fp4 ? B * max_k / 2 : 0), o_xs = take(fp4 ? (size_t)mk_nvfp4_native_scale_bytes((int)B, max_k) : 0);
     h->workspace_bytes = off;
@@ -184,6 +196,8 @@ extern "C" int mk_batched_create(const MkModelDesc *d, int32_t max_batch, void *
     h->qkv_y = (bf16 *)(w + o_qkv); h->up_y = (bf16 *)(w + o_up); h->gate_y = (bf16 *)(w + o_gate);
     h->part_a = (float *)(w + o_pa); h->part_b = (float *)(w + o_pb); h->error_word = (int *)(w + o_err);
     h->x_packed = w + o_xp; h->x_sf = w + o_xs;
+    h->attn_partial = (float *)(w + o_ap);
+    h->covered_dev = (int *)(w + o_cov); h->pos_uniform = (int *)(w + o_pos);
     if (fp4) {
         // native-layout copies of every matrix's block scales
         const int L = d->num_layers;
@@ -215,81 +229,349 @@ extern "C" int mk_batched_create(const MkModelDesc *d, int32_t max_batch, void *
     return 0;
 }
 
+namespace mk {
+namespace {
+
+// Buffers one pass works on: `rows` sequences starting at some cache slot.
+struct StepBuffers {
+    bf16 *hidden, *logits;
+    bf16 *normed_attn, *normed_mlp, *normed_head;  // outputs of the three RMSNorms (may all be the same scratch)
+    bf16 *q, *attn, *act;
+    bf16 *k_cache, *v_cache;                       // already offset to the first sequence's cache slot
+};
+
+// Issues the stream-ordered launches of the operators, one method per opcode of
+// the reference's batched instruction set.  A residual add (o_proj, down_proj) is
+// kept pending and folded into the norm that follows it when there is one.
+struct Runner {
+    BatchedHandle *h;
+    cudaStream_t st;
+    StepBuffers b;
+    const int *pos_ids;
+    int rows;
+    int half_split;   // rotary pairing (see rope_append_kernel)
+    int slice_down;   // add the down projection 2048-column slice by slice (latency interpreter) or as one addend
+    int slot_fixed = -1;  // >= 0: every row reads and appends to this cache slot (rows = tokens of one prompt)
+    bo::LinOut pending;
+    bool has_pending = false;
+    int code = 0;
+
+    bool ok(int c) {
+        if (c != 0 && code == 0) {
+            code = c;
+            if (c < 10000) set_last_error(cudaGetErrorString((cudaError_t)c));
+        }
+        return code == 0;
+    }
+    bo::LinOut result(bf16 *y, float *partials, int n, int splits) const {
+        bo::LinOut o;
+        o.y = y; o.partials = splits > 1 ? partials : nullptr; o.splits = splits; o.batch = rows; o.n = n; o.scale = 1.0f;
+        o.group = 0;
+        return o;
+    }
+    int linear(const bf16 *w, const Fp4Weight *q, const bf16 *x, bf16 *y, float *partials, int n, int k, int splits) {
+        if (!h->fp4)
+            return mk_linear_batched(w, x, splits == 1 ? y : nullptr, splits == 1 ? nullptr : partials, n, k, rows, splits,
+                                     h->error_word, st);
+        // NVFP4: quantise the activation panel (codes + native-layout block scales), then the block-scaled linear
+        const int c = mk_nvfp4_quantize_native(x, h->x_packed, h->x_sf, rows, k, h->act_scale, st);
+        if (c != 0) return c;
+        return mk_linear_batched_nvfp4(q->packed, q->scales_native, q->tensor_scale, h->x_packed, h->x_sf, h->act_scale,
+                                       splits == 1 ? y : nullptr, splits == 1 ? nullptr : partials, n, k, rows, splits,
+                                       h->error_word, st);
+    }
+    void norm(const bf16 *weight, bf16 *normed) {
+        const MkModelDesc &d = h->d;
+        bo::LinOut none = result(nullptr, nullptr, d.hidden_size, 1);
+        ok(launch_residual_norm(b.hidden, has_pending ? pending : none, has_pending ? 1 : 0, weight, normed, rows, d.hidden_size,
+                                d.rms_norm_eps, st));
+        has_pending = false;
+    }
+    void flush() {  // a pending residual add with no norm behind it
+        if (has_pending) norm(nullptr, nullptr);
+    }
+    void attn_norm(int l) {
+        if (code == 0) norm((const bf16 *)h->d.attn_norm_w + (size_t)l * h->d.hidden_size, b.normed_attn);
+    }
+    void qkv(int l) {
+        const MkModelDesc &d = h->d;
+        flush();
+        if (!ok(linear((const bf16 *)d.qkv_w + (size_t)l * h->qkv_rows * d.hidden_size, h->fp4 ? h->w_qkv + l : nullptr,
+                       b.normed_attn, h->qkv_y, h->part_a, h->qkv_rows, d.hidden_size, h->s_qkv)))
+            return;
+        ok(launch_rope_append(result(h->qkv_y, h->part_a, h->qkv_rows, h->s_qkv), pos_ids, d.rope_cos, d.rope_sin, b.q, b.k_cache,
+                              b.v_cache, l, rows, d.kv_batch, d.kv_max_len, d.num_q_heads, d.num_kv_heads, d.head_dim, half_split, slot_fixed, st));
+    }
+    void attention(int l) {
+        const MkModelDesc &d = h->d;
+        flush();
+        if (code) return;
+        ok(launch_attention_batched(b.q, b.k_cache, b.v_cache, pos_ids, b.attn, h->attn_partial,
+                                    attention_batched_splits(rows, d.num_kv_heads, h->sms, kMaxAttnSplits), l, rows, d.kv_batch,
+                                    d.kv_max_len, d.num_q_heads, d.num_kv_heads, d.head_dim, d.attn_scale, slot_fixed, st));
+    }
+    void o_proj(int l) {
+        const MkModelDesc &d = h->d;
+        const int H = d.hidden_size, qd = d.num_q_heads * d.head_dim;
+        flush();
+        if (code) return;
+        if (!ok(linear((const bf16 *)d.o_w + (size_t)l * H * qd, h->fp4 ? h->w_o + l : nullptr, b.attn, h->qkv_y, h->part_a, H, qd,
+                       h->s_o)))
+            return;
+        pending = result(h->qkv_y, h->part_a, H, h->s_o);
+        has_pending = true;
+    }
+    void mlp_norm(int l) {
+        if (code == 0) norm((const bf16 *)h->d.mlp_norm_w + (size_t)l * h->d.hidden_size, b.normed_mlp);
+    }
+    void gate_up(int l, bool with_up) {
+        const MkModelDesc &d = h->d;
+        const int H = d.hidden_size, inter = d.intermediate_size;
+        flush();
+        if (code) return;
+        bo::LinOut up = result(nullptr, nullptr, inter, 1);
+        if (with_up) {
+            if (!ok(linear((const bf16 *)d.up_w + (size_t)l * inter * H, h->fp4 ? h->w_up + l : nullptr, b.normed_mlp, h->up_y,
+                           h->part_a, inter, H, h->s_up)))
+                return;
+            up = result(h->up_y, h->part_a, inter, h->s_up);
+        }
+        if (!ok(linear((const bf16 *)d.gate_w + (size_t)l * inter * H, h->fp4 ? h->w_gate + l : nullptr, b.normed_mlp, h->gate_y,
+                       h->part_b, inter, H, h->s_up)))
+            return;
+        // the quantised model rounds the SiLU product once (tools/analysis/nvfp4/model_reference.py:39-61)
+        ok(launch_silu_mul(up, result(h->gate_y, h->part_b, inter, h->s_up), b.act, rows, inter, h->fp4 ? 0 : 1, st));
+    }
+    void down_proj(int l) {
+        const MkModelDesc &d = h->d;
+        const int H = d.hidden_size, inter = d.intermediate_size;
+        flush();
+        if (code) return;
+        if (!ok(linear((const bf16 *)d.down_w + (size_t)l * H * inter, h->fp4 ? h->w_down + l : nullptr, b.act, h->qkv_y, h->part_a,
+                       H, inter, h->s_down)))
+            return;
+        pending = result(h->qkv_y, h->part_a, H, h->s_down);
+        pending.group = slice_down ? h->down_group : 0;
+        has_pending = true;
+    }
+    void head_norm() {
+        if (code == 0) norm((const bf16 *)h->d.lm_head_norm_w, b.normed_head);
+    }
+    void head() {
+        const MkModelDesc &d = h->d;
+        flush();
+        if (code) return;
+        ok(linear((const bf16 *)d.lm_head_w, h->fp4 ? &h->w_lm : nullptr, b.normed_head, b.logits, nullptr, d.vocab_size,
+                  d.hidden_size, 1));
+    }
+};
+
+}  // namespace
+}  // namespace mk
+
 extern "C" int mk_step_batched(void *handle, const int32_t *tokens_in, const int32_t *pos_ids, int32_t batch,
                                int32_t *tokens_out, void *stream) {
     BatchedHandle *h = (BatchedHandle *)handle;
     if (!h || !tokens_in || !pos_ids) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_step_batched: null argument");
     if (batch < 1 || batch > h->max_batch) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_step_batched: batch outside 1..max_batch");
     const MkModelDesc &d = h->d;
-    cudaStream_t st = (cudaStream_t)stream;
-    const int H = d.hidden_size, D = d.head_dim, L = d.num_layers, inter = d.intermediate_size;
-    const int qd = d.num_q_heads * D;
-    bf16 *hidden = (bf16 *)d.hidden_states;
-    const bf16 *qkv_w = (const bf16 *)d.qkv_w, *o_w = (const bf16 *)d.o_w, *up_w = (const bf16 *)d.up_w;
-    const bf16 *gate_w = (const bf16 *)d.gate_w, *down_w = (const bf16 *)d.down_w;
-    const bf16 *attn_norm = (const bf16 *)d.attn_norm_w, *mlp_norm = (const bf16 *)d.mlp_norm_w;
-
-    // result of linear (n, splits) in the given buffers, as its consumer reads it
-    auto result = [&](bf16 *y, float *partials, int n, int splits) {
-        bo::LinOut o;
-        o.y = y; o.partials = splits > 1 ? partials : nullptr; o.splits = splits; o.batch = batch; o.n = n; o.scale = 1.0f;
-        o.group = 0;
-        return o;
-    };
-    auto linear = [&](const bf16 *w, const Fp4Weight *q, const bf16 *x, bf16 *y, float *partials, int n, int k, int splits) {
-        if (!h->fp4)
-            return mk_linear_batched(w, x, splits == 1 ? y : nullptr, splits == 1 ? nullptr : partials, n, k, batch, splits,
-                                     h->error_word, st);
-        // NVFP4: quantise the activation panel (codes + native-layout block scales), then the block-scaled linear
-        const int code = mk_nvfp4_quantize_native(x, h->x_packed, h->x_sf, batch, k, h->act_scale, st);
-        if (code != 0) return code;
-        return mk_linear_batched_nvfp4(q->packed, q->scales_native, q->tensor_scale, h->x_packed, h->x_sf, h->act_scale,
-                                       splits == 1 ? y : nullptr, splits == 1 ? nullptr : partials, n, k, batch, splits,
-                                       h->error_word, st);
-    };
-    const int round_silu = h->fp4 ? 0 : 1;  // the quantised model rounds the SiLU product once (model_reference.py:39-61)
-#define MK_TRY(expr)                                                             \
-    do {                                                                         \
-        const int code_ = (int)(expr);                                           \
-        if (code_ != 0) {                                                        \
-            if (code_ < 10000) set_last_error(cudaGetErrorString((cudaError_t)code_)); \
-            return code_;                                                        \
-        }                                                                        \
-    } while (0)
-
-    MK_TRY(launch_embed((const bf16 *)d.embed_w, tokens_in, hidden, batch, H, st));
-    bo::LinOut none = result(nullptr, nullptr, H, 1);
-    bo::LinOut down_out = none;
-    for (int l = 0; l < L; ++l) {
-        // pre-attention norm (adds the previous layer's down projection into the residual first)
-        MK_TRY(launch_residual_norm(hidden, down_out, l > 0, attn_norm + (size_t)l * H, h->normed, batch, H, d.rms_norm_eps, st));
-        MK_TRY(linear(qkv_w + (size_t)l * h->qkv_rows * H, h->fp4 ? h->w_qkv + l : nullptr, h->normed, h->qkv_y, h->part_a,
-                      h->qkv_rows, H, h->s_qkv));
-        MK_TRY(launch_rope_append(result(h->qkv_y, h->part_a, h->qkv_rows, h->s_qkv), pos_ids, d.rope_cos, d.rope_sin, h->q,
-                                  (bf16 *)d.k_cache, (bf16 *)d.v_cache, l, d.kv_batch, d.kv_max_len, d.num_q_heads,
-                                  d.num_kv_heads, D, st));
-        MK_TRY(launch_attention_batched(h->q, (const bf16 *)d.k_cache, (const bf16 *)d.v_cache, pos_ids, h->attn, l, d.kv_batch,
-                                        d.kv_max_len, d.num_q_heads, d.num_kv_heads, D, d.attn_scale, st));
-        // o_proj + residual, pre-MLP norm
-        MK_TRY(linear(o_w + (size_t)l * H * qd, h->fp4 ? h->w_o + l : nullptr, h->attn, h->qkv_y, h->part_a, H, qd, h->s_o));
-        MK_TRY(launch_residual_norm(hidden, result(h->qkv_y, h->part_a, H, h->s_o), 1, mlp_norm + (size_t)l * H, h->normed, batch,
-                                    H, d.rms_norm_eps, st));
-        // gate / up + SiLU product
-        MK_TRY(linear(up_w + (size_t)l * inter * H, h->fp4 ? h->w_up + l : nullptr, h->normed, h->up_y, h->part_a, inter, H, h->s_up));
-        MK_TRY(linear(gate_w + (size_t)l * inter * H, h->fp4 ? h->w_gate + l : nullptr, h->normed, h->gate_y, h->part_b, inter, H,
-                      h->s_up));
-        MK_TRY(launch_silu_mul(result(h->up_y, h->part_a, inter, h->s_up), result(h->gate_y, h->part_b, inter, h->s_up), h->act,
-                               batch, inter, round_silu, st));
-        // down_proj; its residual add happens in the next norm
-        MK_TRY(linear(down_w + (size_t)l * H * inter, h->fp4 ? h->w_down + l : nullptr, h->act, h->qkv_y, h->part_a, H, inter,
-                      h->s_down));
-        down_out = result(h->qkv_y, h->part_a, H, h->s_down);
-        down_out.group = h->down_group;
+    if (batch > d.kv_batch) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_step_batched: the cache holds fewer sequences than the batch");
+    Runner r;
+    r.h = h; r.st = (cudaStream_t)stream; r.pos_ids = pos_ids; r.rows = batch; r.half_split = 0; r.slice_down = 1;
+    r.b = StepBuffers{(bf16 *)d.hidden_states, (bf16 *)d.logits, h->normed, h->normed, h->normed, h->q, h->attn, h->act,
+                      (bf16 *)d.k_cache, (bf16 *)d.v_cache};
+    r.ok(launch_embed((const bf16 *)d.embed_w, tokens_in, r.b.hidden, batch, d.hidden_size, r.st));
+    for (int l = 0; l < d.num_layers && r.code == 0; ++l) {
+        r.attn_norm(l); r.qkv(l); r.attention(l); r.o_proj(l); r.mlp_norm(l); r.gate_up(l, true); r.down_proj(l);
     }
-    MK_TRY(launch_residual_norm(hidden, down_out, 1, (const bf16 *)d.lm_head_norm_w, h->normed, batch, H, d.rms_norm_eps, st));
-    MK_TRY(linear((const bf16 *)d.lm_head_w, h->fp4 ? &h->w_lm : nullptr, h->normed, (bf16 *)d.logits, nullptr, d.vocab_size, H, 1));
-    if (tokens_out) MK_TRY(launch_argmax((const bf16 *)d.logits, tokens_out, batch, d.vocab_size, st));
-#undef MK_TRY
+    r.head_norm();
+    r.head();
+    if (tokens_out && r.code == 0) r.ok(launch_argmax((const bf16 *)d.logits, tokens_out, batch, d.vocab_size, r.st));
+    return r.code;
+}
+
+// Prompt processing on the device: the prompt's tokens are the rows of batched passes (up to
+// max_batch tokens each) that all use one cache slot; row i sits at position start_pos + i, its
+// K / V rows are appended before the pass's attention runs, and attention of row i reads rows
+// 0..start_pos + i, which makes it causal.  Replaces the PyTorch forward the reference uses for
+// prefill (megakernels/scripts/generate.py:125-132, llama.py:192-207).
+extern "C" int mk_prefill_batched(void *handle, const int32_t *tokens, int32_t count, int32_t slot, int32_t start_pos,
+                                  int32_t *token_out, void *stream) {
+    BatchedHandle *h = (BatchedHandle *)handle;
+    if (!h || !tokens) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_prefill_batched: null argument");
+    const MkModelDesc &d = h->d;
+    if (count < 1 || slot < 0 || slot >= d.kv_batch || start_pos < 0 || start_pos + count > d.kv_max_len ||
+        start_pos + count > d.rope_positions)
+        return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_prefill_batched: prompt outside the cache / rotary tables, or slot outside the cache");
+    cudaStream_t st = (cudaStream_t)stream;
+    for (int c0 = 0; c0 < count; c0 += h->max_batch) {
+        const int rows = std::min(h->max_batch, count - c0);
+        cudaError_t e = launch_fill_int(h->pos_uniform, start_pos + c0, 1, rows, st);
+        if (e != cudaSuccess) return fail_msg((int)e, cudaGetErrorString(e));
+        Runner r;
+        r.h = h; r.st = st; r.pos_ids = h->pos_uniform; r.rows = rows; r.half_split = 0; r.slice_down = 1; r.slot_fixed = slot;
+        r.b = StepBuffers{(bf16 *)d.hidden_states, (bf16 *)d.logits, h->normed, h->normed, h->normed, h->q, h->attn, h->act,
+                          (bf16 *)d.k_cache, (bf16 *)d.v_cache};
+        r.ok(launch_embed((const bf16 *)d.embed_w, tokens + c0, r.b.hidden, rows, d.hidden_size, st));
+        for (int l = 0; l < d.num_layers && r.code == 0; ++l) {
+            r.attn_norm(l); r.qkv(l); r.attention(l); r.o_proj(l); r.mlp_norm(l); r.gate_up(l, true); r.down_proj(l);
+        }
+        r.flush();
+        if (r.code == 0 && c0 + rows == count && token_out) {
+            // logits and greedy token of the prompt's last position only (row 0 of `logits`)
+            Runner last = r;
+            last.rows = 1;
+            last.b.hidden = r.b.hidden + (size_t)(rows - 1) * d.hidden_size;
+            last.head_norm();
+            last.head();
+            if (last.code == 0) last.ok(launch_argmax((const bf16 *)d.logits, token_out, 1, d.vocab_size, st));
+            r.code = last.code;
+        }
+        if (r.code != 0) return r.code;
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The reference's batched instruction set (opcodes 1-10, megakernels/demos/throughput/
+// instructions.py:57-223) executed at operator granularity: a schedule is accepted when it
+// covers each operator of a layer either completely or not at all, and the covered operators
+// run as the same stream-ordered launches as mk_step_batched, 128 sequences at a time, on the
+// caller's buffers, with one position for the whole batch and the half-split rotary form.
+// ---------------------------------------------------------------------------------------------
+
+extern "C" int mk_throughput_bind(void *handle, const MkThroughputBuffers *buffers) {
+    BatchedHandle *h = (BatchedHandle *)handle;
+    if (!h || !buffers) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_bind: null argument");
+    if (h->max_batch < 128) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_bind: the handle must be created with max_batch 128");
+    if (buffers->batch_size < 128 || buffers->batch_size % 128 || buffers->batch_size > h->d.kv_batch)
+        return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_bind: batch_size must be a multiple of 128 that fits the cache");
+    const void *ptrs[] = {buffers->rms_rope_intermediates, buffers->rms_gate_intermediates, buffers->rms_lm_head_intermediates,
+                          buffers->post_ln_rope_q, buffers->attn_out, buffers->silu_out};
+    for (const void *ptr : ptrs)
+        if (!ptr || (reinterpret_cast<uintptr_t>(ptr) & 15))
+            return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_bind: null or misaligned buffer");
+    if (buffers->barriers && buffers->barrier_cols < std::max(h->d.num_q_heads + 2 * h->d.num_kv_heads, h->d.intermediate_size / 128))
+        return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_bind: barrier rows too short for the QKV heads / intermediate blocks");
+    h->tp = *buffers;
+    h->tp_bound = true;
+    h->plan_ready = false;
+    return 0;
+}
+
+extern "C" int mk_throughput_set_schedule(void *handle, const int32_t *instructions, int32_t workers, int32_t queue_len) {
+    BatchedHandle *h = (BatchedHandle *)handle;
+    if (!h || !instructions) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_set_schedule: null argument");
+    if (!h->tp_bound) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_set_schedule: bind the buffers first (mk_throughput_bind)");
+    if (workers < 1 || queue_len < 1) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_throughput_set_schedule: empty instruction tensor");
+    const MkModelDesc &d = h->d;
+    if (d.hidden_size % 128 || d.intermediate_size % 128 || d.vocab_size % 128 || (d.num_kv_heads * d.head_dim) % 128)
+        return fail_msg(MK_ERR_UNSUPPORTED, "mk_throughput_set_schedule: the instruction set needs hidden, intermediate, vocabulary and K/V widths that are multiples of 128");
+    const size_t words = (size_t)workers * queue_len * 32;
+    std::vector<int32_t> host(words);
+    cudaError_t e = cudaMemcpy(host.data(), instructions, words * sizeof(int32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_msg((int)e, cudaGetErrorString(e));
+    const int L = d.num_layers, B = h->tp.batch_size, nbb = B / 128;
+    const int qkv_blocks = h->qkv_rows / 128, out_blocks = d.hidden_size / 128, inter_blocks = d.intermediate_size / 128;
+    const int vocab_blocks = d.vocab_size / 128;
+    // instructions each operator consists of, and the range of its last operand
+    const long long expect[11] = {0, B, (long long)nbb * qkv_blocks, (long long)B * d.num_kv_heads, (long long)nbb * out_blocks, B,
+                                  (long long)nbb * inter_blocks, (long long)nbb * inter_blocks, (long long)nbb * out_blocks, B,
+                                  (long long)nbb * vocab_blocks};
+    const int last_range[11] = {0, 0, qkv_blocks, d.num_kv_heads, out_blocks, 0, inter_blocks, inter_blocks, out_blocks, 0, vocab_blocks};
+    std::vector<long long> seen((size_t)L * 11, 0);
+    char msg[200];
+    for (int w = 0; w < workers; ++w)
+        for (int s = 0; s < queue_len; ++s) {
+            const int32_t *ins = host.data() + ((size_t)w * queue_len + s) * 32;
+            const int op = ins[0];
+            if (op == 0) continue;
+            bool good = op >= 1 && op <= 10;
+            int layer = 0;
+            if (good) {
+                // operands: (layer, first sequence | sequence block[, block]) - the LM head has no layer
+                const int a = op == 10 ? 0 : ins[1], bidx = op == 10 ? ins[1] : ins[2], c = op == 10 ? ins[2] : ins[3];
+                layer = op >= 9 ? L - 1 : a;
+                const bool per_sequence = op == 1 || op == 3 || op == 5 || op == 9;
+                good = a >= 0 && a < L && bidx >= 0 && bidx < (per_sequence ? B : nbb) &&
+                       (last_range[op] == 0 || (c >= 0 && c < last_range[op]));
+            }
+            if (!good) {
+                snprintf(msg, sizeof(msg), "mk_throughput_set_schedule: worker %d slot %d: opcode %d with operands (%d, %d, %d) is outside the model",
+                         w, s, op, ins[1], ins[2], ins[3]);
+                return fail_msg(MK_ERR_BAD_ARGUMENT, msg);
+            }
+            seen[(size_t)layer * 11 + op] += 1;
+        }
+    std::vector<int> covered(L, 0);
+    for (int l = 0; l < L; ++l)
+        for (int op = 1; op <= 10; ++op) {
+            const long long n = seen[(size_t)l * 11 + op];
+            if (n == 0) continue;
+            if (n != expect[op]) {
+                snprintf(msg, sizeof(msg), "mk_throughput_set_schedule: layer %d opcode %d appears %lld times, the whole operator has %lld instructions (operators run whole or not at all)",
+                         l, op, n, expect[op]);
+                return fail_msg(MK_ERR_UNSUPPORTED, msg);
+            }
+            covered[l] |= 1 << (op - 1);
+        }
+    for (int l = 0; l < L; ++l)
+        if ((covered[l] & (1 << 6)) && !(covered[l] & (1 << 5))) {
+            snprintf(msg, sizeof(msg), "mk_throughput_set_schedule: layer %d has the up matmul (opcode 7) without the gate matmul (opcode 6)", l);
+            return fail_msg(MK_ERR_UNSUPPORTED, msg);
+        }
+    if ((size_t)L > sizeof(h->covered) / sizeof(h->covered[0]))
+        return fail_msg(MK_ERR_UNSUPPORTED, "mk_throughput_set_schedule: more than 256 layers");
+    memcpy(h->covered, covered.data(), L * sizeof(int));
+    e = cudaMemcpy(h->covered_dev, covered.data(), L * sizeof(int), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail_msg((int)e, cudaGetErrorString(e));
+    h->plan_ready = true;
+    return 0;
+}
+
+extern "C" int mk_step_throughput(void *handle, int32_t pos_id, void *stream) {
+    BatchedHandle *h = (BatchedHandle *)handle;
+    if (!h) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_step_throughput: null handle");
+    if (!h->plan_ready) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_step_throughput: no schedule attached (mk_throughput_set_schedule)");
+    const MkModelDesc &d = h->d;
+    if (pos_id < 0 || pos_id >= d.kv_max_len || pos_id >= d.rope_positions)
+        return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_step_throughput: pos_id outside the cache / rotary tables");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int L = d.num_layers, B = h->tp.batch_size, H = d.hidden_size, qd = d.num_q_heads * d.head_dim;
+    cudaError_t e = launch_fill_int(h->pos_uniform, pos_id, 0, 128, st);
+    if (e != cudaSuccess) return fail_msg((int)e, cudaGetErrorString(e));
+    const size_t slot = (size_t)d.kv_max_len * d.num_kv_heads * d.head_dim;  // cache elements per sequence and layer
+    for (int bb = 0; bb < B / 128; ++bb) {
+        const size_t r0 = (size_t)bb * 128;
+        Runner r;
+        r.h = h; r.st = st; r.pos_ids = h->pos_uniform; r.rows = 128; r.half_split = 1; r.slice_down = 0;
+        r.b = StepBuffers{(bf16 *)d.hidden_states + r0 * H, (bf16 *)d.logits + r0 * d.vocab_size,
+                          (bf16 *)h->tp.rms_rope_intermediates + r0 * H, (bf16 *)h->tp.rms_gate_intermediates + r0 * H,
+                          (bf16 *)h->tp.rms_lm_head_intermediates + r0 * H, (bf16 *)h->tp.post_ln_rope_q + r0 * qd,
+                          (bf16 *)h->tp.attn_out + r0 * qd, (bf16 *)h->tp.silu_out + r0 * d.intermediate_size,
+                          (bf16 *)d.k_cache + r0 * slot, (bf16 *)d.v_cache + r0 * slot};
+        for (int l = 0; l < L && r.code == 0; ++l) {
+            const int c = h->covered[l];
+            if (c & 1) r.attn_norm(l);
+            if (c & 2) r.qkv(l);
+            if (c & 4) r.attention(l);
+            if (c & 8) r.o_proj(l);
+            if (c & 16) r.mlp_norm(l);
+            if (c & 32) r.gate_up(l, (c & 64) != 0);
+            if (c & 128) r.down_proj(l);
+            if (l == L - 1) {
+                if (c & 256) r.head_norm();
+                if (c & 512) r.head();
+            }
+        }
+        r.flush();
+        if (r.code != 0) return r.code;
+    }
+    if (h->tp.barriers) {
+        e = launch_barrier_fill((int *)h->tp.barriers, h->covered_dev, L, B, h->tp.barrier_cols, B / 128, d.num_q_heads,
+                                d.num_kv_heads, H / 128, d.intermediate_size / 128, st);
+        if (e != cudaSuccess) return fail_msg((int)e, cudaGetErrorString(e));
+    }
     return 0;
 }
 

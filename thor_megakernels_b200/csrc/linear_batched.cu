@@ -50,6 +50,7 @@
 
 #include "../../include/b200_megakernel.h"
 #include "mk_device.cuh"
+#include "tma_host.cuh"
 
 namespace mk {
 
@@ -349,22 +350,6 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-            res == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
 
 // Row-major matrix [rows, row_bytes] -> boxes of 128 bytes x box_rows rows, 128-byte swizzle.
 // bf16: 64 elements per box row; packed E2M1 codes are moved as bytes (256 codes per box row).

@@ -1,6 +1,7 @@
 """Mode -> builder / interpreter maps (reference ``megakernels/dispatch.py:17-42``).
 
-Only the batch-1 ``latency`` mode exists here.  The reference's PyTorch
+``latency`` is the batch-1 instruction set (the persistent megakernel),
+``throughput`` the batched one (operator-level executor).  The reference's PyTorch
 interpreter (``make_pyvm_interpreter``) is a correctness oracle, not a product
 path; its restatement lives with the tests' oracle and is deliberately not
 reachable from this package.
@@ -11,11 +12,13 @@ from pathlib import Path
 
 from .demos.latency.mk import LatencyMK_Interpreter
 from .demos.latency.scheduler import LatencyScheduleBuilder
+from .demos.throughput.mk import ThroughputMK_Interpreter
+from .demos.throughput.scheduler import ThroughputScheduleBuilder
 from .mk import MK_Interpreter
 from .scheduler import ScheduleBuilder
 
-BUILDER_MAP = {"latency": LatencyScheduleBuilder}
-MK_INTERPRETER_MAP = {"latency": LatencyMK_Interpreter}
+BUILDER_MAP = {"latency": LatencyScheduleBuilder, "throughput": ThroughputScheduleBuilder}
+MK_INTERPRETER_MAP = {"latency": LatencyMK_Interpreter, "throughput": ThroughputMK_Interpreter}
 
 
 def make_schedule_builder(mode: str) -> ScheduleBuilder:

@@ -108,6 +108,19 @@ class MK_FusedGenerator(Generator):
         self.mk = Megakernel.from_globals(globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data,
                                           quantized=quantized)
         globs.barriers.zero_()
+        self._prefiller = None
+
+    def prefill(self, prompt: Tensor, start_pos: int = 0) -> Tensor:
+        """Process the prompt (1-D token ids on the model's device) on the GPU's
+        batched tensor-core path instead of the PyTorch forward the reference uses
+        (megakernels/scripts/generate.py:125-132): fills cache slot 0 at positions
+        ``start_pos ..`` and returns the first generated token (1-element int32
+        tensor).  Runs with the bf16 weights also when decoding is NVFP4."""
+        if self._prefiller is None:
+            from .batched import BatchedDecoder
+
+            self._prefiller = BatchedDecoder(self.model, max_batch=128)
+        return self._prefiller.prefill(prompt.to(torch.int32).contiguous(), slot=0, start_pos=start_pos)
 
     def generate(self, output_tokens: Tensor, prompt_len: int, ntok: int, ntok_already_generated: int = 1):
         assert output_tokens.shape[0] == 1, "batch size must be 1"
