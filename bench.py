@@ -813,7 +813,7 @@ def run_batched(args, rank, world, local):
     steps_per_run, max_ctx = 128, 4096
     peak, peak_src = measured_hbm_peak()
     results = []
-    for batch in (16, 64, 128):
+    for weights, batch in [(w, b) for w in ("bf16", "nvfp4") for b in (16, 64, 128)]:
         extra = ExtraModelConfig(interleave_rope=True, max_len_override=max_ctx + steps_per_run + 8, max_batch_size=batch)
         model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=0, device=device, generate_on=device)
         gen = torch.Generator().manual_seed(3)
@@ -823,7 +823,12 @@ def run_batched(args, rank, world, local):
             for b in range(batch):
                 n = int(lengths[b])
                 cache[:, b, :n] = torch.randn(cache[:, b, :n].shape, generator=dgen, device=device).bfloat16()
-        dec = BatchedDecoder(model, batch)
+        quantized = None
+        if weights == "nvfp4":
+            from thor_megakernels_b200.nvfp4 import quantize_model
+
+            quantized = quantize_model(model)
+        dec = BatchedDecoder(model, batch, quantized=quantized)
         tokens = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).int().to(device)
         start_pos = lengths.int().to(device)
         pos = start_pos.clone()
@@ -859,28 +864,80 @@ def run_batched(args, rank, world, local):
         ms_per_step = start.elapsed_time(end) / (reps * steps_per_run)
         kv = kv_bytes_per_position(cfg)
         kv_bytes = float(sum(kv * (int(n) + steps_per_run / 2 + 1) for n in lengths))   # mean over the run's positions
-        weight_bytes = linear_weight_bytes(cfg)
+        weight_bytes = linear_weight_bytes(cfg) * (0.5625 / 2.0 if weights == "nvfp4" else 1.0)
         gbs = (weight_bytes + kv_bytes) / (ms_per_step * 1e-3) / 1e9
-        flops = 2.0 * batch * (weight_bytes / 2)
-        results.append({"batch": batch, "ms_per_step": ms_per_step, "tokens_per_s": batch / (ms_per_step * 1e-3),
+        flops = 2.0 * batch * (linear_weight_bytes(cfg) / 2)
+        results.append({"weights": weights, "batch": batch, "ms_per_step": ms_per_step, "tokens_per_s": batch / (ms_per_step * 1e-3),
                         "algorithmic_bytes_per_step": weight_bytes + kv_bytes, "kv_share": kv_bytes / (weight_bytes + kv_bytes),
                         "GB/s": gbs, "frac_of_measured_peak": gbs / peak, "linear_TFLOPs": flops / (ms_per_step * 1e-3) / 1e12,
                         "mean_cache_length": float(lengths.float().mean())})
         dec.close()
-        del dec, model
+        del dec, model, quantized
         torch.cuda.empty_cache()
-    best = max(results, key=lambda r: r["tokens_per_s"])
+    best = max((r for r in results if r["weights"] == "bf16"), key=lambda r: r["tokens_per_s"])
     line = {"metric": "decode_tokens_per_s", "value": best["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "llama-3.2-1b-arch bf16 batched greedy decode, 16/64/128 sequences, cache lengths uniform in "
-                                   "[512, 4096] (seed 3), 128 steps per run; value = best batch size",
+            "config": {"workload": "llama-3.2-1b-arch batched greedy decode, 16/64/128 sequences, cache lengths uniform in "
+                                   "[512, 4096] (seed 3), 128 steps per run, bf16 weights and (cases) NVFP4 weights + activations; "
+                                   "value = best bf16 batch size",
                        "step": "one decode step for the whole batch = one CUDA graph replay (tcgen05 linears + batched attention)",
                        "l2": "inputs larger than L2 (weights 2.47 GB + KV 0.6-9.7 GB per step)"},
             "roofline": {"bound": "hbm", "achieved": best["GB/s"], "peak": peak, "unit": "GB/s", "frac": best["GB/s"] / peak,
                          "traffic": None, "peak_source": peak_src},
             "cases": results, "gpu_launches": None, "cpu_baseline": None}
     print(json.dumps(line), flush=True)
+
+
+def run_batched_step(args, rank, world, local):
+    """A few plain (not graph-captured) batched decode steps at one batch size, for a
+    profiler's launch list: --batch sequences, cache lengths as in llama1b-batched,
+    optionally fewer layers (--layers) and NVFP4 weights and activations (--weights nvfp4)."""
+    if rank != 0:
+        return
+    from thor_megakernels_b200.batched import BatchedDecoder
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    cfg = dict(MODEL)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    batch, max_ctx = args.batch, 4096
+    extra = ExtraModelConfig(interleave_rope=True, max_len_override=max_ctx + args.steps + args.warmup + 8, max_batch_size=batch)
+    model = LlamaForCausalLM.random_init(LlamaConfig(**cfg), extra, seed=0, device=device, generate_on=device)
+    gen = torch.Generator().manual_seed(3)
+    lengths = torch.randint(512, max_ctx + 1, (batch,), generator=gen)
+    dgen = torch.Generator(device=device).manual_seed(3)
+    for cache in model.stacked_kv_cache:
+        for b in range(batch):
+            n = int(lengths[b])
+            cache[:, b, :n] = torch.randn(cache[:, b, :n].shape, generator=dgen, device=device).bfloat16()
+    quantized = None
+    if args.weights == "nvfp4":
+        from thor_megakernels_b200.nvfp4 import quantize_model
+
+        quantized = quantize_model(model)
+    dec = BatchedDecoder(model, batch, quantized=quantized)
+    tokens = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).int().to(device)
+    pos = lengths.int().to(device)
+    out = torch.zeros(batch, dtype=torch.int32, device=device)
+    for _ in range(args.warmup):
+        dec.step(tokens, pos, out)
+        pos.add_(1)
+    torch.cuda.synchronize(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        dec.step(tokens, pos, out)
+        pos.add_(1)
+    end.record()
+    torch.cuda.synchronize(device)
+    dec.status()
+    print(json.dumps({"workload": f"batched decode step, {batch} sequences, {cfg['num_hidden_layers']} layers, {args.weights}, "
+                                  "plain launches (no CUDA graph)",
+                      "ms_per_step": start.elapsed_time(end) / args.steps, "steps": args.steps, "warmup": args.warmup}), flush=True)
 
 
 def run_timeline(args, rank, world, local):
@@ -1015,7 +1072,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-8b", action="store_true", help="leave out the nested Llama-3.1-8B record")
     ap.add_argument("--workload", default="llama1b",
-                    choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k", "llama1b-batched", "timeline", "profile-step"],
+                    choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k", "llama1b-batched", "batched-step", "timeline", "profile-step"],
                     help="llama1b: the headline workload (split over the GPUs when N > 1); *-tp: only the split decode")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"], help="weight format (tp, timeline, profile-step)")
     ap.add_argument("--schedule", default="b200", choices=["b200", "rr", "zz", "wave", "dag"],
@@ -1025,6 +1082,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="profile-step: shrink the model to this many layers")
     ap.add_argument("--arch", default="1b", choices=["1b", "8b"], help="profile-step: layer shapes")
     ap.add_argument("--partitions", type=int, default=18, help="profile-step --arch 8b: attention slices per KV head")
+    ap.add_argument("--batch", type=int, default=128, help="batched-step: sequences per step")
     ap.add_argument("--dump", default=None, help="timeline: also save the raw stamps to this .npz file")
     ap.add_argument("--self-test", action="store_true",
                     help="2-layer, 4096-token-vocabulary model to exercise this script quickly; not a benchmark")
@@ -1041,6 +1099,8 @@ def main():
             run_long_context(args, rank, world, local)
         elif args.workload == "llama1b-batched":
             run_batched(args, rank, world, local)
+        elif args.workload == "batched-step":
+            run_batched_step(args, rank, world, local)
         elif args.workload == "timeline":
             run_timeline(args, rank, world, local)
         elif args.workload == "profile-step":

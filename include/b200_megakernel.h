@@ -208,6 +208,11 @@ int mk_query(void *handle, MkLaunchInfo *info);
 int mk_status(void *handle, MkStatus *status, void *stream);
 
 /* Budget of every device-side wait in SM clock cycles (default 4e9). */
+/* After mk_status reported MK_ERR_DEVICE_WAIT: which warps were inside a bounded wait when the launch
+ * gave up.  records receives up to max_records entries of 6 ints (worker, warp, code, opcode, slot,
+ * detail; warp 0 = loader, 1..8 = consumers, 9 = storer; codes as in MkStatus), *count the number of
+ * waiting warps (may exceed max_records).  Clears the record.  Synchronous host copy. */
+int mk_status_detail(void *handle, int32_t *records, int32_t max_records, int32_t *count);
 int mk_set_wait_budget(void *handle, int64_t cycles);
 
 /* Tuning knobs without a counterpart in the reference (its equivalents are
@@ -401,6 +406,11 @@ int mk_batched_status(void *handle, void *stream);
 int mk_prefill_batched(void *handle, const int32_t *tokens, int32_t count, int32_t slot, int32_t start_pos,
                        int32_t *token_out, void *stream);
 int mk_batched_set_activation_scale(void *handle, float tensor_scale);
+/* Process-wide: 1 (default) launches the batched path's kernels (linears, batched operators, prefill, the
+ * batched instruction set, NVFP4 chains) with the programmatic-stream-serialization attribute, so that a
+ * kernel's start-up - for a linear, its first weight tiles - overlaps the tail of the kernel before it;
+ * 0 = plain stream order.  Results do not change. */
+int mk_batched_set_overlap(int32_t enabled);
 void mk_batched_destroy(void *handle);
 
 /*

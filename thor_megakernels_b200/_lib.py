@@ -33,14 +33,14 @@ MK_WEIGHTS_NVFP4 = 1
 
 EXPORTED_SYMBOLS = [
     "mk_last_error", "mk_create", "mk_set_schedule", "mk_step", "mk_query", "mk_status",
-    "mk_set_wait_budget", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
+    "mk_set_wait_budget", "mk_status_detail", "mk_destroy", "mk_nvfp4_quantize", "mk_gemv", "mk_abi_sizeof", "mk_set_option",
     "mk_gemv_static", "mk_tp_init", "mk_tp_connect", "mk_gemv_workspace_bytes",
     "mk_linear_batched", "mk_linear_batched_splits",
     "mk_nvfp4_native_scale_bytes", "mk_nvfp4_quantize_native", "mk_linear_batched_nvfp4",
     "mk_batched_create", "mk_step_batched", "mk_batched_status", "mk_batched_destroy",
     "mk_batched_set_activation_scale",
     "mk_fp4_chain_prepare", "mk_fp4_chain_run", "mk_fp4_chain_status", "mk_fp4_chain_destroy",
-    "mk_prefill_batched", "mk_throughput_bind", "mk_throughput_set_schedule", "mk_step_throughput",
+    "mk_prefill_batched", "mk_batched_set_overlap", "mk_throughput_bind", "mk_throughput_set_schedule", "mk_step_throughput",
 ]
 
 
@@ -151,6 +151,8 @@ def load() -> C.CDLL:
     lib.mk_fp4_chain_status.argtypes = [vp, vp]
     lib.mk_fp4_chain_destroy.argtypes = [vp]
     lib.mk_fp4_chain_destroy.restype = None
+    lib.mk_batched_set_overlap.argtypes = [i32]
+    lib.mk_status_detail.argtypes = [vp, vp, i32, C.POINTER(C.c_int32)]
     lib.mk_prefill_batched.argtypes = [vp, vp, i32, i32, i32, vp, vp]
     lib.mk_throughput_bind.argtypes = [vp, C.POINTER(MkThroughputBuffers)]
     lib.mk_throughput_set_schedule.argtypes = [vp, vp, i32, i32]

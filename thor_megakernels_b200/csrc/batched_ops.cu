@@ -37,6 +37,8 @@ __device__ __forceinline__ float lin_value(const LinOut &o, int b, int i) {
 // hidden[b] = embed[token[b]]
 __global__ void embed_kernel(const bf16 *__restrict__ embed, const int *__restrict__ tokens, bf16 *__restrict__ hidden,
                              int hidden_size) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x;
     const uint4 *src = reinterpret_cast<const uint4 *>(embed + (size_t)__ldg(tokens + b) * hidden_size);
     uint4 *dst = reinterpret_cast<uint4 *>(hidden + (size_t)b * hidden_size);
@@ -53,6 +55,8 @@ __global__ void embed_kernel(const bf16 *__restrict__ embed, const int *__restri
 __global__ void __launch_bounds__(kNormThreads)
 residual_norm_kernel(bf16 *__restrict__ hidden, const LinOut lin, int add, const bf16 *__restrict__ weight,
                      bf16 *__restrict__ normed, int hidden_size, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float row[];  // hidden_size floats
     __shared__ float red[kNormThreads / 32];
     const int b = blockIdx.x;
@@ -101,6 +105,8 @@ __global__ void rope_append_kernel(const LinOut qkv, const int *__restrict__ pos
                                    const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
                                    bf16 *__restrict__ q_out, bf16 *__restrict__ k_cache, bf16 *__restrict__ v_cache,
                                    int layer, int batch, int kv_len, int hq, int hkv, int hd, int half_split, int slot_fixed) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x;
     const int pos = __ldg(pos_ids + b);
     const int q_dim = hq * hd, kv_dim = hkv * hd, total = q_dim + 2 * kv_dim;
@@ -139,41 +145,72 @@ __global__ void rope_append_kernel(const LinOut qkv, const int *__restrict__ pos
 
 // Decode attention of one (sequence, KV head, cache split): the 4 query heads of
 // the group over a contiguous share of cache rows 0..pos (the row appended by this
-// step included).  fp32 scores, softmax and weighted sum.
+// step included), on the tensor cores.
 //
-// The cache rows of the share go through a 4-stage shared-memory pipeline filled
-// with 16-byte asynchronous copies (cp.async) by all 128 threads: every lane moves
-// a different 16 bytes, three stages are in flight while the fourth is consumed,
-// and several CTAs are resident per SM - that is what keeps HBM busy here; at
-// large batch the cache, not the weights, is most of a step's bytes.  A warp takes
-// rows w, w+4, ... of a stage; lane (h = lane/8, sub = lane%8) owns query head h
-// and DPL = D/8 head dimensions and reads its part of a row from shared memory.
+// Data movement: the share's rows go through a shared-memory pipeline (4 stages of
+// 64 rows for 64-wide heads, 3 for 128-wide ones) filled with 16-byte asynchronous
+// copies by all 128 threads; several CTAs are resident per SM, which keeps tens of
+// KiB per SM in flight - at large batch the cache, not the weights, is most of a
+// step's bytes.  16-byte chunk c of row r sits at chunk c ^ (r % 8) of its row, so
+// the 8 rows an ldmatrix phase touches fall into different banks.
+//
+// Arithmetic: warp w owns rows 16w..16w+15 of every stage.  Scores are
+// mma.sync.m16n8k16 with the query heads as M (4 real rows, the rest zero), the
+// cache rows as N and the head dimension as K; K fragments come from ldmatrix.
+// The fp32 score fragment of a thread - head lane/4, rows 2t, 2t+1, 8+2t, 9+2t -
+// is exactly the A fragment of the second product (probabilities x V, V through
+// ldmatrix.trans), so probabilities go from registers to the tensor cores after an
+// online-softmax update (running max in log2 units, rescaled sums).  Scores,
+// softmax and sums are fp32; a probability enters the second product as two bf16
+// terms (value + remainder), which keeps about 16 of its significant bits.
 //
 // splits == 1: the merged result leaves as bf16 attention output.  Otherwise each
 // split writes its unnormalised state (max in log2 units, sum, output) to
 // `partial` [batch, Hq, splits, D + 2] and attention_merge_kernel combines them.
 constexpr int kAttnWarps = 4;
-constexpr int kAttnStages = 4;
-// cache rows per stage: 32 for 64-wide heads, 16 for 128-wide ones (8 KiB of K + V per stage either way)
+constexpr int kAttnRows = 64;   // cache rows per stage: 16 per warp
 
-__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst_smem)), "l"(src) : "memory");
+template <int D>
+struct AttnShape {
+    static constexpr int kStages = D == 64 ? 4 : 3;
+    static constexpr int kRowBytes = D * 2, kChunksPerRow = D / 8;
+    static constexpr int kStageBytes = kAttnRows * kRowBytes;   // per K (and per V)
+    static constexpr int kPartFloats = kAttnWarps * 4 * (D + 2);
+    static constexpr size_t kSmemBytes = (size_t)2 * kStages * kStageBytes + kPartFloats * sizeof(float);
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// d += a x b; rows 8..15 of a (fragments a1, a3) are zero here
+__device__ __forceinline__ void mma_bf16_top(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
-template <int DPL>
+template <int D>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attention_batched_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ k_cache, const bf16 *__restrict__ v_cache,
                          const int *__restrict__ pos_ids, bf16 *__restrict__ out, float *__restrict__ partial, int splits,
                          int layer, int cache_batch, int kv_len, int hq, int hkv, float attn_scale, int slot_fixed) {
-    constexpr int V = DPL / 8, D = DPL * 8;
-    constexpr int kAttnRows = DPL == 8 ? 32 : 16;
-    constexpr int kRowBytes = D * 2, kStageBytes = kAttnRows * kRowBytes;  // per K (and per V)
-    __shared__ __align__(16) uint8_t stage_k[kAttnStages][kStageBytes];
-    __shared__ __align__(16) uint8_t stage_v[kAttnStages][kStageBytes];
-    __shared__ float part[kAttnWarps][4][D + 2];
+    pdl_launch_dependents();
+    pdl_wait();
+    using S = AttnShape<D>;
+    extern __shared__ __align__(128) uint8_t attn_smem[];
+    uint8_t *stage_k = attn_smem, *stage_v = attn_smem + S::kStages * S::kStageBytes;
+    float(*part)[4][D + 2] = reinterpret_cast<float(*)[4][D + 2]>(attn_smem + 2 * S::kStages * S::kStageBytes);
     const int kv_head = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = lane >> 3, sub = lane & 7, d0 = sub * DPL;
+    const int g = lane >> 2, t = lane & 3;
     const int seq_len = __ldg(pos_ids + b) + 1;
     // this split's share of the rows, in whole stages
     const int stages_total = (seq_len + kAttnRows - 1) / kAttnRows;
@@ -183,103 +220,129 @@ attention_batched_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ k_
     const int n_stages = t_end > t_begin ? (t_end - t_begin + kAttnRows - 1) / kAttnRows : 0;
     const size_t tok_stride = (size_t)hkv * D;
     const size_t base = (((size_t)layer * cache_batch + (slot_fixed >= 0 ? slot_fixed : b)) * kv_len) * tok_stride + (size_t)kv_head * D;
-    const bf16 *kbase = k_cache + base, *vbase = v_cache + base;
+    const uint8_t *kbase = reinterpret_cast<const uint8_t *>(k_cache + base), *vbase = reinterpret_cast<const uint8_t *>(v_cache + base);
+    const uint32_t sk = smem_addr(stage_k), sv = smem_addr(stage_v);
 
-    // one stage = kAttnRows rows of K and of V; chunk c of 16 bytes: row c / (kRowBytes/16), offset c % ...
-    constexpr int kChunksPerRow = kRowBytes / 16, kChunks = kAttnRows * kChunksPerRow;
     auto fill = [&](int st_idx) {
-        const int slot = st_idx % kAttnStages, t0 = t_begin + st_idx * kAttnRows;
-        for (int c = threadIdx.x; c < kChunks; c += kAttnWarps * 32) {
-            const int r = c / kChunksPerRow, o = (c % kChunksPerRow) * 16;
+        const int slot = st_idx % S::kStages, t0 = t_begin + st_idx * kAttnRows;
+        for (int c = threadIdx.x; c < kAttnRows * S::kChunksPerRow; c += kAttnWarps * 32) {
+            const int r = c / S::kChunksPerRow, ch = c % S::kChunksPerRow;
+            const uint32_t off = slot * S::kStageBytes + r * S::kRowBytes + ((ch ^ (r & 7)) << 4);
             if (t0 + r < t_end) {
-                cp_async16(&stage_k[slot][r * kRowBytes + o], reinterpret_cast<const uint8_t *>(kbase + (size_t)(t0 + r) * tok_stride) + o);
-                cp_async16(&stage_v[slot][r * kRowBytes + o], reinterpret_cast<const uint8_t *>(vbase + (size_t)(t0 + r) * tok_stride) + o);
+                const size_t src = (size_t)(t0 + r) * tok_stride * 2 + ch * 16;
+                cp_async16(sk + off, kbase + src);
+                cp_async16(sv + off, vbase + src);
+            } else {  // rows past the share: zeros, so that they add nothing (and no NaN) to either product
+                *reinterpret_cast<uint4 *>(stage_k + off) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(stage_v + off) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    // prologue: stages 0 .. kAttnStages-2 in flight (empty groups keep the counting uniform)
-    for (int i = 0; i < kAttnStages - 1; ++i) {
+    // prologue: stages 0 .. kStages-2 in flight (empty groups keep the counting uniform)
+    for (int i = 0; i < S::kStages - 1; ++i) {
         if (i < n_stages) fill(i);
         else asm volatile("cp.async.commit_group;" ::: "memory");
     }
 
-    float qf[DPL];
-    {
-        const bf16 *qp = q + (size_t)b * hq * D + (size_t)(kv_head * 4 + h) * D + d0;
+    // query fragments: head g (lanes with g < 4), dimensions 16 ks + {2t, 2t+1} and + 8
+    uint32_t qa[D / 16][2];
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            float tmp[8];
-            unpack8(*reinterpret_cast<const uint4 *>(qp + 8 * v), tmp);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) qf[8 * v + i] = tmp[i];
+    for (int ks = 0; ks < D / 16; ++ks) {
+        qa[ks][0] = qa[ks][1] = 0u;
+        if (g < 4) {
+            const bf16 *qp = q + (size_t)b * hq * D + (size_t)(kv_head * 4 + g) * D + ks * 16 + 2 * t;
+            qa[ks][0] = *reinterpret_cast<const uint32_t *>(qp);
+            qa[ks][1] = *reinterpret_cast<const uint32_t *>(qp + 8);
         }
     }
-    float m = -INFINITY, l = 0.f, acc[DPL];
+    float m = -INFINITY, l = 0.f;
+    float o[D / 8][4];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     const float scale_log2e = attn_scale * 1.4426950408889634f;
+    const int r0 = warp * 16;                 // this warp's rows within a stage
+    const int lrow = lane & 7, lmat = lane >> 3;  // ldmatrix: this lane addresses row lrow of matrix lmat
 
     for (int st_idx = 0; st_idx < n_stages; ++st_idx) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(kAttnStages - 2) : "memory");  // stage st_idx has landed (for this thread)
-        __syncthreads();                                                              // ... and for everybody; stage st_idx-1 is free
-        if (st_idx + kAttnStages - 1 < n_stages) fill(st_idx + kAttnStages - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(S::kStages - 2) : "memory");  // stage st_idx has landed (for this thread)
+        __syncthreads();                                                           // ... and for everybody; stage st_idx-1 is free
+        if (st_idx + S::kStages - 1 < n_stages) fill(st_idx + S::kStages - 1);
         else asm volatile("cp.async.commit_group;" ::: "memory");
-        const int slot = st_idx % kAttnStages, t0 = t_begin + st_idx * kAttnRows;
-        const int rows = min(kAttnRows, t_end - t0);
-        // a warp's rows of this stage: w, w+4, ...; all scores first, one running-max update, then the sums
-        constexpr int kPerWarp = kAttnRows / kAttnWarps;
-        float sc[kPerWarp];
+        const int slot = st_idx % S::kStages, t0 = t_begin + st_idx * kAttnRows;
+        const int rows = t_end - t0;          // valid rows of this stage (may exceed 64)
+        if (r0 >= rows) continue;             // warp-uniform: nothing of this stage belongs to the warp
+        const uint32_t kb = sk + slot * S::kStageBytes, vb = sv + slot * S::kStageBytes;
+
+        // scores[head][row]: two 8-row tiles, K dimension = head dimension
+        float sc[2][4];
 #pragma unroll
-        for (int j = 0; j < kPerWarp; ++j) {
-            const int r = warp + j * kAttnWarps;
-            float d = 0.f;
-            if (r < rows) {
+        for (int nt = 0; nt < 2; ++nt) {
+            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+            const int r = r0 + nt * 8 + lrow;
 #pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    float kf[8];
-                    unpack8(*reinterpret_cast<const uint4 *>(&stage_k[slot][r * kRowBytes + d0 * 2 + 16 * v]), kf);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) d = fmaf(qf[8 * v + i], kf[i], d);
-                }
+            for (int k2 = 0; k2 < D / 32; ++k2) {   // one ldmatrix.x4 = chunks 4 k2 .. 4 k2 + 3 = two K steps
+                uint32_t kf[4];
+                ldmatrix_x4(kb + r * S::kRowBytes + (((4 * k2 + lmat) ^ (r & 7)) << 4), kf);
+                mma_bf16_top(sc[nt], qa[2 * k2][0], qa[2 * k2][1], kf[0], kf[1]);
+                mma_bf16_top(sc[nt], qa[2 * k2 + 1][0], qa[2 * k2 + 1][1], kf[2], kf[3]);
             }
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            d += __shfl_xor_sync(0xffffffffu, d, 2);
-            d += __shfl_xor_sync(0xffffffffu, d, 4);
-            sc[j] = r < rows ? d * scale_log2e : -INFINITY;
         }
-        float mn = m;
+        // online softmax for head g over rows r0 + {2t, 2t+1, 8+2t, 9+2t}
+        float sv4[4];
 #pragma unroll
-        for (int j = 0; j < kPerWarp; ++j) mn = fmaxf(mn, sc[j]);
-        if (mn > -INFINITY) {   // this warp has at least one row so far
-            const float corr = exp2f(m - mn);  // exp2(-inf) = 0 the first time
-            l *= corr;
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+            for (int e = 0; e < 2; ++e)
+                sv4[2 * nt + e] = (r0 + nt * 8 + 2 * t + e < rows) ? sc[nt][e] * scale_log2e : -INFINITY;
+        float mx = fmaxf(fmaxf(sv4[0], sv4[1]), fmaxf(sv4[2], sv4[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mn = fmaxf(m, mx);                                    // finite: the warp has at least one valid row
+        const float corr = (m == -INFINITY) ? 0.f : exp2f(m - mn);
+        float pr[4];
 #pragma unroll
-            for (int j = 0; j < kPerWarp; ++j) {
-                const int r = warp + j * kAttnWarps;
-                if (r < rows) {
-                    const float pr = exp2f(sc[j] - mn);
-                    l += pr;
+        for (int i = 0; i < 4; ++i) pr[i] = (g < 4 && sv4[i] > -INFINITY) ? exp2f(sv4[i] - mn) : 0.f;
+        l = l * corr + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+        m = mn;
 #pragma unroll
-                    for (int v = 0; v < V; ++v) {
-                        float vf[8];
-                        unpack8(*reinterpret_cast<const uint4 *>(&stage_v[slot][r * kRowBytes + d0 * 2 + 16 * v]), vf);
+        for (int i = 0; i < D / 8; ++i) { o[i][0] *= corr; o[i][1] *= corr; }
+        // The tensor core takes bf16 operands; a probability goes in as the sum of two bf16
+        // values (the rounded value and the rounded remainder, about 16 significant bits), so
+        // the weighted sum keeps fp32-like accuracy at the cost of a second MMA per tile.
+        uint32_t pa_hi[2], pa_lo[2];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[8 * v + i] = fmaf(pr, vf[i], acc[8 * v + i]);
-                    }
-                }
-            }
-            m = mn;
+        for (int i = 0; i < 2; ++i) {
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(pr[2 * i], pr[2 * i + 1]);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(pr[2 * i] - __low2float(hi), pr[2 * i + 1] - __high2float(hi));
+            pa_hi[i] = *reinterpret_cast<const uint32_t *>(&hi);
+            pa_lo[i] = *reinterpret_cast<const uint32_t *>(&lo);
+        }
+        // out[head][d] += p[head][row] * V[row][d]: 16 rows as K, 8 dimensions per tile, two tiles per ldmatrix
+#pragma unroll
+        for (int d2 = 0; d2 < D / 16; ++d2) {
+            uint32_t vf[4];
+            const int r = r0 + (lmat & 1) * 8 + lrow;
+            ldmatrix_x4_trans(vb + r * S::kRowBytes + (((2 * d2 + (lmat >> 1)) ^ (r & 7)) << 4), vf);
+            mma_bf16_top(o[2 * d2], pa_hi[0], pa_hi[1], vf[0], vf[1]);
+            mma_bf16_top(o[2 * d2], pa_lo[0], pa_lo[1], vf[0], vf[1]);
+            mma_bf16_top(o[2 * d2 + 1], pa_hi[0], pa_hi[1], vf[2], vf[3]);
+            mma_bf16_top(o[2 * d2 + 1], pa_lo[0], pa_lo[1], vf[2], vf[3]);
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (g < 4) {
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) part[warp][h][d0 + i] = acc[i];
-    if (sub == 0) {
-        part[warp][h][D] = m;
-        part[warp][h][D + 1] = l;
+        for (int i = 0; i < D / 8; ++i) {
+            part[warp][g][i * 8 + 2 * t] = o[i][0];
+            part[warp][g][i * 8 + 2 * t + 1] = o[i][1];
+        }
+        if (t == 0) {
+            part[warp][g][D] = m;
+            part[warp][g][D + 1] = l;
+        }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < 4 * D; idx += kAttnWarps * 32) {
@@ -311,6 +374,8 @@ attention_batched_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ k_
 
 // Combines the splits of one (sequence, query head): weights exp2(m_s - max m), one thread per head dimension.
 __global__ void attention_merge_kernel(const float *__restrict__ partial, bf16 *__restrict__ out, int splits, int hq, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const float *src = partial + (((size_t)b * hq + head) * splits) * (D + 2);
     float M = -INFINITY;
@@ -329,6 +394,8 @@ __global__ void attention_merge_kernel(const float *__restrict__ partial, bf16 *
 // results (an `up` without buffers counts as 1: SiLU only).  With `round_silu` 0 the product is rounded once (the rule of the
 // reference's quantised model, tools/analysis/nvfp4/model_reference.py:39-61).
 __global__ void silu_mul_kernel(const LinOut up, const LinOut gate, bf16 *__restrict__ act, int batch, int inter, int round_silu) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t total = (size_t)batch * inter;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const int b = (int)(idx / inter), i = (int)(idx % inter);
@@ -342,6 +409,8 @@ __global__ void silu_mul_kernel(const LinOut up, const LinOut gate, bf16 *__rest
 
 // token[b] = argmax_i logits[b, i], lowest index on ties.  One CTA per sequence.
 __global__ void __launch_bounds__(256) argmax_kernel(const bf16 *__restrict__ logits, int *__restrict__ tokens, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ unsigned long long best_s[8];
     const int b = blockIdx.x;
     unsigned long long best = 0ull;
@@ -369,29 +438,28 @@ __global__ void __launch_bounds__(256) argmax_kernel(const bf16 *__restrict__ lo
 
 // launchers used by the batched step (batched_step.cu); declared in batched_ops.cuh
 cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int batch, int hidden_size, cudaStream_t st) {
-    bo::embed_kernel<<<batch, 128, 0, st>>>(embed, tokens, hidden, hidden_size);
-    return cudaGetLastError();
+    return launch_pdl(bo::embed_kernel, dim3(batch), dim3(128), 0, st, embed, tokens, hidden, hidden_size);
 }
 
 cudaError_t launch_residual_norm(bf16 *hidden, const bo::LinOut &lin, int add, const bf16 *weight, bf16 *normed, int batch,
                                  int hidden_size, float eps, cudaStream_t st) {
-    bo::residual_norm_kernel<<<batch, bo::kNormThreads, hidden_size * sizeof(float), st>>>(hidden, lin, add, weight, normed,
-                                                                                             hidden_size, eps);
-    return cudaGetLastError();
+    return launch_pdl(bo::residual_norm_kernel, dim3(batch), dim3(bo::kNormThreads), hidden_size * sizeof(float), st, hidden, lin, add,
+                      weight, normed, hidden_size, eps);
 }
 
 cudaError_t launch_rope_append(const bo::LinOut &qkv, const int *pos_ids, const float *rope_cos, const float *rope_sin, bf16 *q_out,
                                bf16 *k_cache, bf16 *v_cache, int layer, int rows, int cache_batch, int kv_len, int hq, int hkv,
                                int hd, int half_split, int slot_fixed, cudaStream_t st) {
-    bo::rope_append_kernel<<<rows, 256, 0, st>>>(qkv, pos_ids, rope_cos, rope_sin, q_out, k_cache, v_cache, layer, cache_batch,
-                                                  kv_len, hq, hkv, hd, half_split, slot_fixed);
-    return cudaGetLastError();
+    return launch_pdl(bo::rope_append_kernel, dim3(rows), dim3(256), 0, st, qkv, pos_ids, rope_cos, rope_sin, q_out, k_cache, v_cache,
+                      layer, cache_batch, kv_len, hq, hkv, hd, half_split, slot_fixed);
 }
 
 namespace bo {
 
 // dst[i] = value + i * step
 __global__ void fill_int_kernel(int *__restrict__ dst, int value, int step, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = value + i * step;
 }
@@ -403,6 +471,8 @@ __global__ void fill_int_kernel(int *__restrict__ dst, int value, int step, int 
 // has bit (opcode - 1) set for covered operators.
 __global__ void barrier_fill_kernel(int *__restrict__ barriers, const int *__restrict__ covered, int batch, int cols,
                                     int batch_blocks, int hq, int hkv, int out_blocks, int inter_blocks) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int layer = blockIdx.x / 10, op = blockIdx.x % 10;  // op = opcode - 1
     if (!((covered[layer] >> op) & 1)) return;
     int *base = barriers + ((size_t)layer * 10 + op) * batch * cols;
@@ -422,15 +492,13 @@ __global__ void barrier_fill_kernel(int *__restrict__ barriers, const int *__res
 }  // namespace bo
 
 cudaError_t launch_fill_int(int *dst, int value, int step, int n, cudaStream_t st) {
-    bo::fill_int_kernel<<<(n + 255) / 256, 256, 0, st>>>(dst, value, step, n);
-    return cudaGetLastError();
+    return launch_pdl(bo::fill_int_kernel, dim3((n + 255) / 256), dim3(256), 0, st, dst, value, step, n);
 }
 
 cudaError_t launch_barrier_fill(int *barriers, const int *covered, int layers, int batch, int cols, int batch_blocks, int hq,
                                 int hkv, int out_blocks, int inter_blocks, cudaStream_t st) {
-    bo::barrier_fill_kernel<<<layers * 10, 128, 0, st>>>(barriers, covered, batch, cols, batch_blocks, hq, hkv, out_blocks,
-                                                        inter_blocks);
-    return cudaGetLastError();
+    return launch_pdl(bo::barrier_fill_kernel, dim3(layers * 10), dim3(128), 0, st, barriers, covered, batch, cols, batch_blocks, hq, hkv,
+                      out_blocks, inter_blocks);
 }
 
 // Cache splits per (sequence, KV head): enough CTAs to fill the GPU a few times over at small
@@ -441,20 +509,34 @@ int attention_batched_splits(int batch, int hkv, int sms, int max_splits) {
     return splits;
 }
 
+template <int D>
+static cudaError_t launch_attention_d(dim3 grid, cudaStream_t st, const bf16 *q, const bf16 *k_cache, const bf16 *v_cache, const int *pos_ids,
+                                      bf16 *out, float *partial, int splits, int layer, int cache_batch, int kv_len, int hq, int hkv,
+                                      float attn_scale, int slot_fixed) {
+    static bool configured[64] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 64 && !configured[device]) {
+        e = cudaFuncSetAttribute(bo::attention_batched_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)bo::AttnShape<D>::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[device] = true;
+    }
+    return launch_pdl(bo::attention_batched_kernel<D>, grid, dim3(bo::kAttnWarps * 32), bo::AttnShape<D>::kSmemBytes, st, q, k_cache,
+                      v_cache, pos_ids, out, partial, splits, layer, cache_batch, kv_len, hq, hkv, attn_scale, slot_fixed);
+}
+
 cudaError_t launch_attention_batched(const bf16 *q, const bf16 *k_cache, const bf16 *v_cache, const int *pos_ids, bf16 *out,
                                      float *partial, int splits, int layer, int batch, int cache_batch, int kv_len, int hq, int hkv,
                                      int hd, float attn_scale, int slot_fixed, cudaStream_t st) {
-    const dim3 grid(hkv, batch, splits), block(bo::kAttnWarps * 32);
-    if (hd == 64)
-        bo::attention_batched_kernel<8><<<grid, block, 0, st>>>(q, k_cache, v_cache, pos_ids, out, partial, splits, layer,
-                                                                 cache_batch, kv_len, hq, hkv, attn_scale, slot_fixed);
-    else
-        bo::attention_batched_kernel<16><<<grid, block, 0, st>>>(q, k_cache, v_cache, pos_ids, out, partial, splits, layer,
-                                                                  cache_batch, kv_len, hq, hkv, attn_scale, slot_fixed);
-    cudaError_t e = cudaGetLastError();
+    const dim3 grid(hkv, batch, splits);
+    cudaError_t e = hd == 64 ? launch_attention_d<64>(grid, st, q, k_cache, v_cache, pos_ids, out, partial, splits, layer, cache_batch,
+                                                      kv_len, hq, hkv, attn_scale, slot_fixed)
+                             : launch_attention_d<128>(grid, st, q, k_cache, v_cache, pos_ids, out, partial, splits, layer, cache_batch,
+                                                       kv_len, hq, hkv, attn_scale, slot_fixed);
     if (e != cudaSuccess || splits == 1) return e;
-    bo::attention_merge_kernel<<<dim3(hq, batch), hd, 0, st>>>(partial, out, splits, hq, hd);
-    return cudaGetLastError();
+    return launch_pdl(bo::attention_merge_kernel, dim3(hq, batch), dim3(hd), 0, st, partial, out, splits, hq, hd);
 }
 
 cudaError_t launch_silu_mul(const bo::LinOut &up, const bo::LinOut &gate, bf16 *act, int batch, int inter, int round_silu,
@@ -462,13 +544,21 @@ cudaError_t launch_silu_mul(const bo::LinOut &up, const bo::LinOut &gate, bf16 *
     const size_t total = (size_t)batch * inter;
     const size_t want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
-    bo::silu_mul_kernel<<<blocks, 256, 0, st>>>(up, gate, act, batch, inter, round_silu);
-    return cudaGetLastError();
+    return launch_pdl(bo::silu_mul_kernel, dim3(blocks), dim3(256), 0, st, up, gate, act, batch, inter, round_silu);
 }
 
 cudaError_t launch_argmax(const bf16 *logits, int *tokens, int batch, int vocab, cudaStream_t st) {
-    bo::argmax_kernel<<<batch, 256, 0, st>>>(logits, tokens, vocab);
-    return cudaGetLastError();
+    return launch_pdl(bo::argmax_kernel, dim3(batch), dim3(256), 0, st, logits, tokens, vocab);
 }
 
+static bool g_launch_overlap = true;
+bool launch_overlap_enabled() { return g_launch_overlap; }
+
 }  // namespace mk
+
+// 1 (default): the batched path's kernels are launched with the programmatic-stream-
+// serialization attribute; 0: plain stream order.  Results do not change.
+extern "C" int mk_batched_set_overlap(int32_t enabled) {
+    mk::g_launch_overlap = enabled != 0;
+    return 0;
+}

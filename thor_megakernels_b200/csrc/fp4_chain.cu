@@ -21,6 +21,7 @@
 #include <vector>
 
 #include "../../include/b200_megakernel.h"
+#include "batched_ops.cuh"
 
 extern "C" int32_t mk_linear_batched_splits(int32_t n, int32_t k, int32_t sm_count);
 
@@ -52,6 +53,8 @@ int fail_chain(int code, const char *text) {
 
 // y[b, i] = bf16(sum_s partials[s, b, i])
 __global__ void fold_partials_kernel(const float *__restrict__ partials, __nv_bfloat16 *__restrict__ y, int splits, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
         float v = 0.f;
         for (int s = 0; s < splits; ++s) v += partials[(size_t)s * total + idx];
@@ -136,8 +139,8 @@ extern "C" int mk_fp4_chain_run(void *handle, void *stream) {
         if (op.splits > 1) {
             const long long total = (long long)c->batch * o.m;
             const int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
-            fold_partials_kernel<<<blocks, 256, 0, st>>>(op.partials, (__nv_bfloat16 *)o.output, op.splits, total);
-            const cudaError_t e = cudaGetLastError();
+            const cudaError_t e = launch_pdl(fold_partials_kernel, dim3(blocks), dim3(256), 0, st, (const float *)op.partials,
+                                             (__nv_bfloat16 *)o.output, op.splits, total);
             if (e != cudaSuccess) return fail_chain((int)e, cudaGetErrorString(e));
         }
     }

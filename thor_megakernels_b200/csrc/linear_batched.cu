@@ -50,6 +50,7 @@
 
 #include "../../include/b200_megakernel.h"
 #include "mk_device.cuh"
+#include "batched_ops.cuh"
 #include "tma_host.cuh"
 
 namespace mk {
@@ -195,6 +196,7 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     static_assert(kStageK == 64 || kStageK == 256, "one 128-byte swizzle row per stage");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *failed = &s.failed;
+    pdl_launch_dependents();  // the next kernel on the stream may start its own prologue
     const uint32_t acc_cols = (uint32_t)p.batch_pad;       // fp32 columns of one accumulator
     // two accumulators, then (NVFP4) 16 columns of weight scales and 16 of activation scales
     const uint32_t sf_base = acc_cols * 2;
@@ -232,23 +234,56 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             uint64_t keep_policy;                                    // activations: re-read by every CTA
             asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep_policy));
             uint32_t stage = 0, phase = 0, filled = 0;  // filled: stages that have been filled at least once
-            for (int item = blockIdx.x; item < items && !*failed; item += gridDim.x) {
-                const int slab = item / p.splits, split = item % p.splits;
-                const int kb0 = split * p.kblocks_per_split;
-                for (int kb = kb0; kb < kb0 + p.kblocks_per_split; ++kb) {
-                    if (!wait_bounded(&s.empty[stage], phase ^ 1u, failed)) break;
-                    filled |= 1u << stage;
-                    mbar_arrive_expect_tx(&s.full[stage], stage_tx);
-                    // x coordinate in elements of the map's type: bf16 columns, or bytes of packed codes (128 per stage)
-                    const int x = FP4 ? kb * 128 : kb * kBlockK;
-                    tma_load_2d(s.stage[stage].a, &map_w, x, slab * kSlabRows, &s.full[stage], stream_policy);
-                    tma_load_2d(s.stage[stage].b, &map_x, x, 0, &s.full[stage], keep_policy);
-                    if constexpr (FP4) {
-                        bulk_load(s.stage[stage].sfa, p.sfa + ((size_t)slab * p.kblocks + kb) * kSfBytes, kSfBytes, &s.full[stage], stream_policy);
-                        bulk_load(s.stage[stage].sfb, p.sfb + (size_t)kb * kSfBytes, kSfBytes, &s.full[stage], keep_policy);
-                    }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            // fills in order: (item, K block) pairs of this CTA
+            struct Fill { int item, kb, kb_end; };
+            auto first_fill = [&]() {
+                Fill f{(int)blockIdx.x, 0, 0};
+                if (f.item < items) { f.kb = (f.item % p.splits) * p.kblocks_per_split; f.kb_end = f.kb + p.kblocks_per_split; }
+                return f;
+            };
+            auto next_fill = [&](Fill &f) {
+                if (++f.kb == f.kb_end) {
+                    f.item += gridDim.x;
+                    if (f.item < items) { f.kb = (f.item % p.splits) * p.kblocks_per_split; f.kb_end = f.kb + p.kblocks_per_split; }
                 }
+            };
+            // weights (and their scales) do not depend on the kernel before this one; activations do
+            auto load_weights = [&](const Fill &f, uint32_t st) {
+                const int slab = f.item / p.splits;
+                const int x = FP4 ? f.kb * 128 : f.kb * kBlockK;  // bf16 columns, or bytes of packed codes (128 per stage)
+                tma_load_2d(s.stage[st].a, &map_w, x, slab * kSlabRows, &s.full[st], stream_policy);
+                if constexpr (FP4)
+                    bulk_load(s.stage[st].sfa, p.sfa + ((size_t)slab * p.kblocks + f.kb) * kSfBytes, kSfBytes, &s.full[st], stream_policy);
+            };
+            auto load_activations = [&](const Fill &f, uint32_t st) {
+                const int x = FP4 ? f.kb * 128 : f.kb * kBlockK;
+                tma_load_2d(s.stage[st].b, &map_x, x, 0, &s.full[st], keep_policy);
+                if constexpr (FP4) bulk_load(s.stage[st].sfb, p.sfb + (size_t)f.kb * kSfBytes, kSfBytes, &s.full[st], keep_policy);
+            };
+            // Prologue: the weight tiles of the first STAGES fills are requested before the
+            // predecessor kernel has finished (every stage is free at the start); their
+            // activation tiles follow once it has.
+            Fill f = first_fill();
+            {
+                Fill g = f;
+                int n = 0;
+                for (; n < STAGES && g.item < items; ++n, next_fill(g)) {
+                    filled |= 1u << n;
+                    mbar_arrive_expect_tx(&s.full[n], stage_tx);
+                    load_weights(g, n);
+                }
+                pdl_wait();
+                for (int i = 0; i < n; ++i, next_fill(f)) load_activations(f, i);
+                stage = n == STAGES ? 0 : n;
+                phase = n == STAGES ? 1u : 0u;
+            }
+            for (; f.item < items && !*failed; next_fill(f)) {
+                if (!wait_bounded(&s.empty[stage], phase ^ 1u, failed)) break;
+                filled |= 1u << stage;
+                mbar_arrive_expect_tx(&s.full[stage], stage_tx);
+                load_weights(f, stage);
+                load_activations(f, stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
             // Never leave with copies in flight.  In a clean run the MMA warp has waited for every
             // fill; after a failure, wait here (bounded) for the most recent fill of every stage.
@@ -306,6 +341,7 @@ linear_batched_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         __syncwarp();
     } else {
         // epilogue: warp w may touch tensor-memory lanes 32*(w % 4) .. +31
+        pdl_wait();  // the output buffer may still be read by the kernels before this one
         const int quarter = warp & 3;
         uint32_t acc = 0, acc_phase = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x) {
@@ -417,7 +453,8 @@ static int launch(const void *w, const void *x, const uint8_t *sfa, const uint8_
     }
     const int items = p.slabs * splits;
     const int grid = items < sms ? items : sms;
-    linear_batched_kernel<kStages, FP4><<<grid, kThreads, smem, stream>>>(map_w, map_x, p);
+    e = launch_pdl(linear_batched_kernel<kStages, FP4>, dim3(grid), dim3(kThreads), smem, stream, map_w, map_x, p);
+    if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
 
@@ -427,6 +464,8 @@ static int launch(const void *w, const void *x, const uint8_t *sfa, const uint8_
 // 512-byte atoms the tensor core reads.
 __global__ void quantize_native_kernel(const bf16 *__restrict__ input, uint8_t *__restrict__ packed, uint8_t *__restrict__ sf,
                                        int rows, int k, float tensor_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int groups_per_row = k / 16;
     const long long grp = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (grp >= (long long)rows * groups_per_row) return;
@@ -493,9 +532,9 @@ extern "C" int mk_nvfp4_quantize_native(const void *input_bf16, void *packed, vo
     }
     const long long groups = (long long)rows * (k / 16);
     const int threads = 256;
-    mk::lb::quantize_native_kernel<<<(unsigned)((groups + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
-        (const mk::bf16 *)input_bf16, (uint8_t *)packed, (uint8_t *)scales_native, rows, k, tensor_scale);
-    return (int)cudaGetLastError();
+    return (int)mk::launch_pdl(mk::lb::quantize_native_kernel, dim3((unsigned)((groups + threads - 1) / threads)), dim3(threads), 0,
+                               (cudaStream_t)stream, (const mk::bf16 *)input_bf16, (uint8_t *)packed, (uint8_t *)scales_native, rows, k,
+                               tensor_scale);
 }
 
 extern "C" int mk_linear_batched_nvfp4(const void *w_packed, const void *w_scales_native, float w_tensor_scale, const void *x_packed,

@@ -153,6 +153,7 @@ struct Params {
     unsigned long long *argmax_key;
     int *done_counter;
     int *status;                    // [0] code [1] worker [2] opcode [3] slot [4] detail [5] expected [7] abort
+    int *stuck;                     // [worker][warp][4]: the wait a warp was in when the launch aborted (code, opcode, slot, detail)
     const int *token_in;
     int *token_out;
 };
@@ -179,8 +180,20 @@ struct __align__(128) Smem {
 
 __device__ __forceinline__ bool aborted(const Smem &s) { return *reinterpret_cast<const volatile int *>(&s.abort_flag) != 0; }
 
+// Where this warp was waiting when the launch gave up (first record per warp and failure wins).
+__device__ __noinline__ void note_stuck(const Params &p, const Smem &s, int code, int opcode, int slot, int detail) {
+    if (*reinterpret_cast<const volatile int *>(&s.abort_flag) == 2) return;  // the failure happened in an earlier launch
+    int *rec = p.stuck + ((size_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * 4;
+    if (atomicCAS(rec, 0, code) == 0) {
+        rec[1] = opcode;
+        rec[2] = slot;
+        rec[3] = detail;
+    }
+}
+
 __device__ __noinline__ void report_failure(const Params &p, Smem &s, int code, int opcode, int slot, int detail,
                                             int expected) {
+    note_stuck(p, s, code, opcode, slot, detail);
     if (atomicCAS(&p.status[0], 0, code) == 0) {
         p.status[1] = blockIdx.x;
         p.status[2] = opcode;
@@ -202,9 +215,10 @@ __device__ __forceinline__ void wait_mbar(const Params &p, Smem &s, uint64_t *ba
     unsigned it = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++it & 31u) == 0) {
-            if (aborted(s)) return;
+            if (aborted(s)) { note_stuck(p, s, code, opcode, slot, detail); return; }
             if ((it & 1023u) == 0 && ld_relaxed_gpu(&p.status[7]) != 0) {
                 *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+                note_stuck(p, s, code, opcode, slot, detail);
                 return;
             }
             if (clock64() - t0 > p.spin_cycles) {
@@ -230,9 +244,10 @@ __device__ __forceinline__ void wait_counter(const Params &p, Smem &s, const int
         v = ld_relaxed_gpu(ctr);
         if (v >= expected) return;
         if ((++it & 15u) == 0) {
-            if (aborted(s)) return;
+            if (aborted(s)) { note_stuck(p, s, kFailCounter, opcode, slot, v); return; }
             if (ld_relaxed_gpu(&p.status[7]) != 0) {
                 *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+                note_stuck(p, s, kFailCounter, opcode, slot, v);
                 return;
             }
             if (clock64() - t0 > p.spin_cycles) {
@@ -258,9 +273,10 @@ __device__ __forceinline__ Deadline start_deadline() { return Deadline{clock64()
 __device__ __forceinline__ bool keep_waiting(const Params &p, Smem &s, Deadline &d, int opcode, int slot, int detail) {
     __nanosleep(40);
     if ((++d.it & 7u) == 0) {
-        if (aborted(s)) return false;
+        if (aborted(s)) { note_stuck(p, s, kFailData, opcode, slot, detail); return false; }
         if (ld_relaxed_gpu(&p.status[7]) != 0) {
             *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+            note_stuck(p, s, kFailData, opcode, slot, detail);
             return false;
         }
         if (clock64() - d.t0 > p.spin_cycles) {
@@ -314,9 +330,10 @@ __device__ __noinline__ uint4 load8_slow(const Params &p, Smem &s, const unsigne
         a0 = b0; a1 = b1;
         b0 = ld_tagged2(cells); b1 = ld_tagged2(cells + 2);
         if ((++d.it & 15u) == 0) {
-            if (aborted(s)) break;
+            if (aborted(s)) { note_stuck(p, s, kFailData, opcode, slot, 8); break; }
             if (ld_relaxed_gpu(&p.status[7]) != 0) {
                 *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+                note_stuck(p, s, kFailData, opcode, slot, 8);
                 break;
             }
             if (clock64() - d.t0 > p.spin_cycles) {
@@ -580,8 +597,13 @@ __device__ void loader_role(const Params &p, Smem &s, long long t_start) {
         // Keep at most `max_inflight` tiles outstanding: more than the memory system
         // needs to stay busy only lengthens its queues, and with them the latency of
         // the small loads on the dependency path between SMs.
+        // The fills not yet seen to have landed must never span a whole turn of the ring:
+        // mbar_try_wait tells phases apart by parity only, so a fill may not be issued
+        // into a stage while the previous fill of that same stage is still unobserved
+        // (once the new fill lands, the old phase's parity reads "not complete" again).
+        const int inflight_limit = p.max_inflight < F::stages ? p.max_inflight : F::stages;
         while (outstanding > 0 && mbar_try_wait(&s.full[land.stage], land.phase)) { land.advance(); --outstanding; }
-        while (outstanding >= p.max_inflight && !aborted(s)) {
+        while (outstanding >= inflight_limit && !aborted(s)) {
             wait_mbar(p, s, &s.full[land.stage], land.phase, kFailRing, t.opcode, t.slot, (int)land.stage);
             land.advance();
             --outstanding;
@@ -1761,7 +1783,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const Params p
             mbar_init(&s.pfull[i], kConsumerWarps);
             mbar_init(&s.pempty[i], 1);
         }
-        s.abort_flag = 0;
+        // a launch that follows a failed one (status not yet read by the host) does no work: every wait falls through
+        s.abort_flag = ld_relaxed_gpu(&p.status[7]) != 0 ? 2 : 0;
         s.is_last = 0;
         fence_barrier_init();
     }
@@ -2008,7 +2031,9 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     const size_t cells = n_resid + n_hidden + n_down + n_q + 2 * n_kv + n_attn + n_silu + n_oi + n_lse;
     const size_t cell_bytes = (cells * sizeof(unsigned long long) + 255) & ~size_t(255);
     const size_t table_entries = fp4 ? 5 * L + 1 : 0;  // device copies of the quantised-matrix tables
-    h->scratch_bytes = cell_bytes + 256 + table_entries * sizeof(MkNvfp4Matrix);
+    const size_t table_bytes = (table_entries * sizeof(MkNvfp4Matrix) + 255) & ~size_t(255);
+    const size_t stuck_bytes = (size_t)h->sm_count * (kThreads / 32) * 4 * sizeof(int);
+    h->scratch_bytes = cell_bytes + 256 + table_bytes + stuck_bytes;
     e = cudaMalloc(&h->scratch, h->scratch_bytes);
     if (e != cudaSuccess) { delete h; return cuda_fail(e, "cudaMalloc(scratch)"); }
     e = cudaMemset(h->scratch, 0, h->scratch_bytes);  // tag 0 is never a launch tag
@@ -2062,6 +2087,7 @@ extern "C" int mk_create(const MkModelDesc *d, void **out) {
     p.done_counter = (int *)(sc + cell_bytes + 16);
     p.status = (int *)(sc + cell_bytes + 32);
     p.epoch = (unsigned *)(sc + cell_bytes + 64);
+    p.stuck = (int *)(sc + cell_bytes + 256 + table_bytes);
     p.model_numerics = fp4 ? 1 : 0;
     p.tp_rank = 0; p.tp_world = 1; p.vocab_offset = 0;
     if (fp4) {
@@ -2256,6 +2282,29 @@ extern "C" int mk_status(void *handle, MkStatus *status, void *stream) {
         return fail(MK_ERR_DEVICE_WAIT, "device wait expired: code %d worker %d opcode %d slot %d saw %d expected %d",
                     words[0], words[1], words[2], words[3], words[4], words[5]);
     }
+    return 0;
+}
+
+extern "C" int mk_status_detail(void *handle, int32_t *records, int32_t max_records, int32_t *count) {
+    Handle *h = (Handle *)handle;
+    if (!h || !records || max_records < 0 || !count) return fail(MK_ERR_BAD_ARGUMENT, "mk_status_detail: bad argument");
+    const int warps = kThreads / 32, total = h->sm_count * warps;
+    int32_t *all = new (std::nothrow) int32_t[(size_t)total * 4];
+    if (!all) return fail(MK_ERR_BAD_ARGUMENT, "mk_status_detail: out of host memory");
+    cudaError_t e = cudaMemcpy(all, h->params.stuck, (size_t)total * 4 * sizeof(int32_t), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemset(h->params.stuck, 0, (size_t)total * 4 * sizeof(int32_t));
+    if (e != cudaSuccess) { delete[] all; return cuda_fail(e, "mk_status_detail"); }
+    int n = 0;
+    for (int i = 0; i < total; ++i) {
+        if (all[4 * i] == 0) continue;
+        if (n < max_records) {
+            int32_t *r = records + 6 * n;
+            r[0] = i / warps; r[1] = i % warps; r[2] = all[4 * i]; r[3] = all[4 * i + 1]; r[4] = all[4 * i + 2]; r[5] = all[4 * i + 3];
+        }
+        ++n;
+    }
+    delete[] all;
+    *count = n;
     return 0;
 }
 

@@ -213,4 +213,14 @@ __device__ __forceinline__ float warp_reduce16(float (&acc)[16], int lane) {
     return acc[0] + __shfl_xor_sync(0xffffffffu, acc[0], 1);
 }
 
+
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-
+// serialization attribute may start while its predecessor on the stream is still
+// running.  pdl_launch_dependents() lets the successor start early; pdl_wait()
+// returns once the predecessor has completed and its writes are visible (a no-op
+// for a kernel launched without the attribute).  Everything a kernel reads from or
+// writes to buffers that other kernels touch comes after pdl_wait().
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 }  // namespace mk

@@ -208,6 +208,15 @@ class Megakernel:
             raise err
         return out
 
+    def stuck_warps(self, max_records: int = 2048) -> list[dict]:
+        """After ``status()`` raised: the bounded wait every waiting warp was in
+        (worker, warp, code, opcode, slot, detail)."""
+        buf = (C.c_int32 * (6 * max_records))()
+        n = C.c_int32(0)
+        _lib.check(self.lib.mk_status_detail(self.handle, buf, max_records, C.byref(n)))
+        names = ("worker", "warp", "code", "opcode", "slot", "detail")
+        return [dict(zip(names, buf[6 * i : 6 * i + 6])) for i in range(min(n.value, max_records))]
+
     # -- tensor parallelism ------------------------------------------------
     def tp_init(self, rank: int, world: int, vocab_offset: int) -> bytes:
         """Allocates this GPU's exchange buffer; returns its CUDA IPC handle (64
