@@ -22,6 +22,7 @@ namespace mk {
 namespace bo {
 
 constexpr int kNormThreads = 256;
+constexpr int kNormVecs = 8;   // float4 groups per thread: hidden sizes up to 8192
 
 // LinOut (batched_ops.cuh) is the result of a batched linear as its consumers
 // read it: bf16 y [batch, n], or the fp32 split-K partial sums [splits, batch, n],
@@ -32,6 +33,49 @@ __device__ __forceinline__ float lin_value(const LinOut &o, int b, int i) {
     float total = 0.f;
     for (int s = 0; s < o.splits; ++s) total += o.partials[((size_t)s * o.batch + b) * o.n + i];
     return round_bf16(total * o.scale);
+}
+
+// Two / four consecutive elements (i even / a multiple of 4): vector loads, the splits'
+// loads independent of one another so that they are in flight together.
+__device__ __forceinline__ float2 lin_value2(const LinOut &o, int b, int i) {
+    if (o.partials == nullptr) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(o.y + (size_t)b * o.n + i));
+    float2 total = make_float2(0.f, 0.f);
+#pragma unroll 4
+    for (int s = 0; s < o.splits; ++s) {
+        const float2 v = *reinterpret_cast<const float2 *>(o.partials + ((size_t)s * o.batch + b) * o.n + i);
+        total.x += v.x; total.y += v.y;
+    }
+    return make_float2(round_bf16(total.x * o.scale), round_bf16(total.y * o.scale));
+}
+
+__device__ __forceinline__ float4 load_bf16x4(const bf16 *p) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store_bf16x4(bf16 *p, const float4 &v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t *>(&a);
+    raw.y = *reinterpret_cast<const uint32_t *>(&b);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+// sum of splits [s0, s1) for elements i..i+3, times the scale, rounded to bf16
+__device__ __forceinline__ float4 partial_sum4(const LinOut &o, int b, int i, int s0, int s1) {
+    float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = s0; s < s1; ++s) {
+        const float4 v = *reinterpret_cast<const float4 *>(o.partials + ((size_t)s * o.batch + b) * o.n + i);
+        total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+    }
+    return make_float4(round_bf16(total.x * o.scale), round_bf16(total.y * o.scale), round_bf16(total.z * o.scale),
+                       round_bf16(total.w * o.scale));
+}
+__device__ __forceinline__ float4 lin_value4(const LinOut &o, int b, int i) {
+    if (o.partials == nullptr) return load_bf16x4(o.y + (size_t)b * o.n + i);
+    return partial_sum4(o, b, i, 0, o.splits);
 }
 
 // hidden[b] = embed[token[b]]
@@ -57,26 +101,32 @@ residual_norm_kernel(bf16 *__restrict__ hidden, const LinOut lin, int add, const
                      bf16 *__restrict__ normed, int hidden_size, float eps) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float row[];  // hidden_size floats
     __shared__ float red[kNormThreads / 32];
     const int b = blockIdx.x;
+    const int vecs = hidden_size / 4;   // a thread owns elements 4v..4v+3 for v = tid, tid + 256, ... (at most kNormVecs of them)
+    float4 h[kNormVecs];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden_size; i += kNormThreads) {
-        float h = __bfloat162float(hidden[(size_t)b * hidden_size + i]);
-        if (add) {
-            if (lin.partials != nullptr && lin.group > 0) {
-                for (int s0 = 0; s0 < lin.splits; s0 += lin.group) {
-                    float total = 0.f;
-                    for (int sp = s0; sp < s0 + lin.group; ++sp) total += lin.partials[((size_t)sp * lin.batch + b) * lin.n + i];
-                    h = round_bf16(h + round_bf16(total * lin.scale));
+#pragma unroll
+    for (int j = 0; j < kNormVecs; ++j) {
+        const int v = threadIdx.x + j * kNormThreads;
+        h[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (v < vecs) {
+            bf16 *hp = hidden + (size_t)b * hidden_size + 4 * v;
+            float4 x = load_bf16x4(hp);
+            if (add) {
+                auto add_rounded = [&](const float4 &y) {
+                    x = make_float4(round_bf16(x.x + y.x), round_bf16(x.y + y.y), round_bf16(x.z + y.z), round_bf16(x.w + y.w));
+                };
+                if (lin.partials != nullptr && lin.group > 0) {
+                    for (int s0 = 0; s0 < lin.splits; s0 += lin.group) add_rounded(partial_sum4(lin, b, 4 * v, s0, s0 + lin.group));
+                } else {
+                    add_rounded(lin_value4(lin, b, 4 * v));
                 }
-            } else {
-                h = round_bf16(h + lin_value(lin, b, i));
+                store_bf16x4(hp, x);
             }
-            hidden[(size_t)b * hidden_size + i] = __float2bfloat16_rn(h);
+            h[j] = x;
+            ss = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, fmaf(x.w, x.w, ss))));
         }
-        row[i] = h;
-        ss = fmaf(h, h, ss);
     }
     if (normed == nullptr) return;
 #pragma unroll
@@ -87,9 +137,15 @@ residual_norm_kernel(bf16 *__restrict__ hidden, const LinOut lin, int add, const
 #pragma unroll
     for (int w = 0; w < kNormThreads / 32; ++w) total += red[w];
     const float rstd = 1.0f / sqrtf(total / (float)hidden_size + eps);
-    for (int i = threadIdx.x; i < hidden_size; i += kNormThreads) {
-        const float w = __bfloat162float(weight[i]);
-        normed[(size_t)b * hidden_size + i] = __float2bfloat16_rn(w * round_bf16(row[i] * rstd));
+#pragma unroll
+    for (int j = 0; j < kNormVecs; ++j) {
+        const int v = threadIdx.x + j * kNormThreads;
+        if (v < vecs) {
+            const float4 w = load_bf16x4(weight + 4 * v);
+            store_bf16x4(normed + (size_t)b * hidden_size + 4 * v,
+                         make_float4(w.x * round_bf16(h[j].x * rstd), w.y * round_bf16(h[j].y * rstd), w.z * round_bf16(h[j].z * rstd),
+                                     w.w * round_bf16(h[j].w * rstd)));
+        }
     }
 }
 
@@ -109,36 +165,47 @@ __global__ void rope_append_kernel(const LinOut qkv, const int *__restrict__ pos
     pdl_wait();
     const int b = blockIdx.x;
     const int pos = __ldg(pos_ids + b);
-    const int q_dim = hq * hd, kv_dim = hkv * hd, total = q_dim + 2 * kv_dim;
+    const int q_dim = hq * hd, kv_dim = hkv * hd, total = q_dim + 2 * kv_dim, half = hd / 2;
     // cache slot: the row's own (batched decode) or one slot for all rows (the rows are tokens of one prompt)
     const size_t cache_row = (((size_t)layer * batch + (slot_fixed >= 0 ? slot_fixed : b)) * kv_len + pos) * kv_dim;
-    auto store = [&](int i, float y) {
-        const bf16 v = __float2bfloat16_rn(y);
-        if (i < q_dim) q_out[(size_t)b * q_dim + i] = v;
-        else if (i < q_dim + kv_dim) k_cache[cache_row + (i - q_dim)] = v;
-        else v_cache[cache_row + (i - q_dim - kv_dim)] = v;
+    auto store2 = [&](int i, float y0, float y1) {   // elements i, i + 1 of the row (i even)
+        const __nv_bfloat162 v = __floats2bfloat162_rn(y0, y1);
+        if (i < q_dim) *reinterpret_cast<__nv_bfloat162 *>(q_out + (size_t)b * q_dim + i) = v;
+        else if (i < q_dim + kv_dim) *reinterpret_cast<__nv_bfloat162 *>(k_cache + cache_row + (i - q_dim)) = v;
+        else *reinterpret_cast<__nv_bfloat162 *>(v_cache + cache_row + (i - q_dim - kv_dim)) = v;
     };
-    for (int pair = threadIdx.x; pair < total / 2; pair += blockDim.x) {
-        const int half = hd / 2;
-        const int i0 = half_split ? (pair / half) * hd + pair % half : 2 * pair;
-        const int i1 = half_split ? i0 + half : i0 + 1;
-        const float x0 = lin_value(qkv, b, i0), x1 = lin_value(qkv, b, i1);
-        float y0 = x0, y1 = x1;
-        if (i0 < q_dim + kv_dim) {
-            const int d0 = i0 % hd, d1 = i1 % hd;
-            const float c0 = __ldg(rope_cos + (size_t)pos * hd + d0), s0 = __ldg(rope_sin + (size_t)pos * hd + d0);
-            const float c1 = __ldg(rope_cos + (size_t)pos * hd + d1), s1 = __ldg(rope_sin + (size_t)pos * hd + d1);
-            y0 = round_bf16(__fadd_rn(__fmul_rn(x0, c0), __fmul_rn(-x1, s0)));
-            y1 = round_bf16(__fadd_rn(__fmul_rn(x1, c1), __fmul_rn(x0, s1)));
-        }
-        if (!half_split) {
-            const __nv_bfloat162 out = __floats2bfloat162_rn(y0, y1);
-            if (i0 < q_dim) *reinterpret_cast<__nv_bfloat162 *>(q_out + (size_t)b * q_dim + i0) = out;
-            else if (i0 < q_dim + kv_dim) *reinterpret_cast<__nv_bfloat162 *>(k_cache + cache_row + (i0 - q_dim)) = out;
-            else *reinterpret_cast<__nv_bfloat162 *>(v_cache + cache_row + (i0 - q_dim - kv_dim)) = out;
+    // a unit = two rotation pairs = two 2-element loads A and B:
+    //   adjacent pairs: A = (i, i+1), B = (i+2, i+3), pairs (A.x, A.y), (B.x, B.y)
+    //   half-split:     A = (i, i+1), B = (i+half, i+half+1), pairs (A.x, B.x), (A.y, B.y)
+    for (int unit = threadIdx.x; unit < total / 4; unit += blockDim.x) {
+        int ia, ib;
+        if (half_split) {
+            const int head = unit / (half / 2), j = 2 * (unit % (half / 2));
+            ia = head * hd + j;
+            ib = ia + half;
         } else {
-            store(i0, y0);
-            store(i1, y1);
+            ia = 4 * unit;
+            ib = ia + 2;
+        }
+        const float2 A = lin_value2(qkv, b, ia), B = lin_value2(qkv, b, ib);
+        if (ia >= q_dim + kv_dim) {   // V: copied
+            store2(ia, A.x, A.y);
+            store2(ib, B.x, B.y);
+            continue;
+        }
+        const int da = ia % hd, db = ib % hd;
+        const float2 ca = *reinterpret_cast<const float2 *>(rope_cos + (size_t)pos * hd + da);
+        const float2 sa = *reinterpret_cast<const float2 *>(rope_sin + (size_t)pos * hd + da);
+        const float2 cb = *reinterpret_cast<const float2 *>(rope_cos + (size_t)pos * hd + db);
+        const float2 sb = *reinterpret_cast<const float2 *>(rope_sin + (size_t)pos * hd + db);
+        auto rot0 = [](float x0, float x1, float c, float s_) { return round_bf16(__fadd_rn(__fmul_rn(x0, c), __fmul_rn(-x1, s_))); };
+        auto rot1 = [](float x0, float x1, float c, float s_) { return round_bf16(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s_))); };
+        if (half_split) {   // pairs (A.x, B.x) and (A.y, B.y); first elements use the tables at da, second at db
+            store2(ia, rot0(A.x, B.x, ca.x, sa.x), rot0(A.y, B.y, ca.y, sa.y));
+            store2(ib, rot1(A.x, B.x, cb.x, sb.x), rot1(A.y, B.y, cb.y, sb.y));
+        } else {            // pairs (A.x, A.y) and (B.x, B.y)
+            store2(ia, rot0(A.x, A.y, ca.x, sa.x), rot1(A.x, A.y, ca.y, sa.y));
+            store2(ib, rot0(B.x, B.y, cb.x, sb.x), rot1(B.x, B.y, cb.y, sb.y));
         }
     }
 }
@@ -190,13 +257,6 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-// d += a x b; rows 8..15 of a (fragments a1, a3) are zero here
-__device__ __forceinline__ void mma_bf16_top(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
-}
-
 template <int D>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attention_batched_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ k_cache, const bf16 *__restrict__ v_cache,
@@ -396,30 +456,48 @@ __global__ void attention_merge_kernel(const float *__restrict__ partial, bf16 *
 __global__ void silu_mul_kernel(const LinOut up, const LinOut gate, bf16 *__restrict__ act, int batch, int inter, int round_silu) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t total = (size_t)batch * inter;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int b = (int)(idx / inter), i = (int)(idx % inter);
-        const float g = lin_value(gate, b, i);
-        const float u = (up.y == nullptr && up.partials == nullptr) ? 1.0f : lin_value(up, b, i);
-        float a = g / (1.0f + expf(-g));
-        if (round_silu) a = round_bf16(a);
-        act[idx] = __float2bfloat16_rn(a * u);
+    const size_t total4 = (size_t)batch * inter / 4;   // four consecutive elements per thread and iteration
+    const bool no_up = up.y == nullptr && up.partials == nullptr;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += (size_t)gridDim.x * blockDim.x) {
+        const int b = (int)(4 * idx / inter), i = (int)(4 * idx % inter);
+        const float4 g = lin_value4(gate, b, i);
+        const float4 u = no_up ? make_float4(1.f, 1.f, 1.f, 1.f) : lin_value4(up, b, i);
+        auto f = [&](float gv, float uv) {
+            float a = gv / (1.0f + expf(-gv));
+            if (round_silu) a = round_bf16(a);
+            return a * uv;
+        };
+        store_bf16x4(act + 4 * idx, make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w)));
     }
 }
 
 // token[b] = argmax_i logits[b, i], lowest index on ties.  One CTA per sequence.
-__global__ void __launch_bounds__(256) argmax_kernel(const bf16 *__restrict__ logits, int *__restrict__ tokens, int vocab) {
+constexpr int kArgmaxThreads = 1024;
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_kernel(const bf16 *__restrict__ logits, int *__restrict__ tokens, int vocab) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ unsigned long long best_s[8];
+    __shared__ unsigned long long best_s[kArgmaxThreads / 32];
     const int b = blockIdx.x;
+    const bf16 *row = logits + (size_t)b * vocab;
     unsigned long long best = 0ull;
-    for (int i = threadIdx.x; i < vocab; i += 256) {
-        uint32_t bits = (uint32_t)__bfloat16_as_ushort(logits[(size_t)b * vocab + i]);
+    auto consider = [&](uint32_t bits, int i) {
         bits = (bits & 0x8000u) ? (~bits & 0xffffu) : (bits | 0x8000u);  // order-preserving
         const unsigned long long key = ((unsigned long long)bits << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i);
         if (key > best) best = key;
+    };
+    // 16-byte loads (8 logits) while the row allows it, the remainder one by one
+    const int vec_end = ((reinterpret_cast<uintptr_t>(row) & 15) == 0) ? (vocab / 8) * 8 : 0;
+#pragma unroll 4
+    for (int i = 8 * threadIdx.x; i < vec_end; i += 8 * kArgmaxThreads) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(row + i));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            consider(w[j] & 0xffffu, i + 2 * j);
+            consider(w[j] >> 16, i + 2 * j + 1);
+        }
     }
+    for (int i = vec_end + threadIdx.x; i < vocab; i += kArgmaxThreads) consider((uint32_t)__bfloat16_as_ushort(row[i]), i);
 #pragma unroll
     for (int off = 16; off; off >>= 1) {
         const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, off);
@@ -428,7 +506,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const bf16 *__restrict__ lo
     if ((threadIdx.x & 31) == 0) best_s[threadIdx.x >> 5] = best;
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < 8; ++w)
+        for (int w = 1; w < kArgmaxThreads / 32; ++w)
             if (best_s[w] > best) best = best_s[w];
         tokens[b] = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
     }
@@ -443,8 +521,9 @@ cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int
 
 cudaError_t launch_residual_norm(bf16 *hidden, const bo::LinOut &lin, int add, const bf16 *weight, bf16 *normed, int batch,
                                  int hidden_size, float eps, cudaStream_t st) {
-    return launch_pdl(bo::residual_norm_kernel, dim3(batch), dim3(bo::kNormThreads), hidden_size * sizeof(float), st, hidden, lin, add,
-                      weight, normed, hidden_size, eps);
+    if (hidden_size % 4 || hidden_size > 4 * bo::kNormThreads * bo::kNormVecs) return cudaErrorInvalidValue;
+    return launch_pdl(bo::residual_norm_kernel, dim3(batch), dim3(bo::kNormThreads), 0, st, hidden, lin, add, weight, normed, hidden_size,
+                      eps);
 }
 
 cudaError_t launch_rope_append(const bo::LinOut &qkv, const int *pos_ids, const float *rope_cos, const float *rope_sin, bf16 *q_out,
@@ -504,8 +583,10 @@ cudaError_t launch_barrier_fill(int *barriers, const int *covered, int layers, i
 // Cache splits per (sequence, KV head): enough CTAs to fill the GPU a few times over at small
 // batch, none at large batch; at most `max_splits` (what the caller's partial buffer holds).
 int attention_batched_splits(int batch, int hkv, int sms, int max_splits) {
+    // 8 CTAs' worth of work per SM: with three CTAs resident per SM and cache lengths that differ by up to 8x
+    // between sequences, smaller shares even out the last wave
     int splits = 1;
-    while (batch * hkv * splits < 4 * sms && splits * 2 <= max_splits) splits *= 2;
+    while (batch * hkv * splits < 8 * sms && splits * 2 <= max_splits) splits *= 2;
     return splits;
 }
 
@@ -541,14 +622,14 @@ cudaError_t launch_attention_batched(const bf16 *q, const bf16 *k_cache, const b
 
 cudaError_t launch_silu_mul(const bo::LinOut &up, const bo::LinOut &gate, bf16 *act, int batch, int inter, int round_silu,
                             cudaStream_t st) {
-    const size_t total = (size_t)batch * inter;
+    const size_t total = (size_t)batch * inter / 4;
     const size_t want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
     return launch_pdl(bo::silu_mul_kernel, dim3(blocks), dim3(256), 0, st, up, gate, act, batch, inter, round_silu);
 }
 
 cudaError_t launch_argmax(const bf16 *logits, int *tokens, int batch, int vocab, cudaStream_t st) {
-    return launch_pdl(bo::argmax_kernel, dim3(batch), dim3(256), 0, st, logits, tokens, vocab);
+    return launch_pdl(bo::argmax_kernel, dim3(batch), dim3(bo::kArgmaxThreads), 0, st, logits, tokens, vocab);
 }
 
 static bool g_launch_overlap = true;

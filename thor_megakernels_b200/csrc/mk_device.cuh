@@ -214,6 +214,23 @@ __device__ __forceinline__ float warp_reduce16(float (&acc)[16], int lane) {
 }
 
 
+// d += a x b for mma.sync.m16n8k16 (bf16 operands, fp32 accumulation) when rows 8..15
+// of a - its fragments a1 and a3 - are zero.
+__device__ __forceinline__ void mma_bf16_top(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+// The same with the caller keeping only the top half of the accumulator: z0, z1 stand for rows 8..15,
+// which stay zero and may be shared between any number of accumulators.
+__device__ __forceinline__ void mma_bf16_top(float &d0, float &d1, float &z0, float &z1, uint32_t a0, uint32_t a2, uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d0), "+f"(d1), "+f"(z0), "+f"(z1)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
 // Programmatic dependent launch: a kernel launched with the programmatic-stream-
 // serialization attribute may start while its predecessor on the stream is still
 // running.  pdl_launch_dependents() lets the successor start early; pdl_wait()
