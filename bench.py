@@ -161,7 +161,20 @@ def dist_setup(n_gpus: int):
         backend = "nccl" if torch.cuda.is_available() else "gloo"
         if torch.cuda.is_available():
             torch.cuda.set_device(local)
-        dist.init_process_group(backend=backend)
+        # NCCL prints its version banner on standard output when the first communicator is created; this
+        # script's standard output carries one JSON line and nothing else, so the banner goes to stderr.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group(backend=backend)
+            dist.barrier()
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     return rank, world, local
 
 
@@ -182,10 +195,20 @@ def max_over_ranks(x: float, world: int) -> float:
     return float(t.item())
 
 
+def pick_schedule(requested: str, weights: str = "bf16") -> str:
+    """``auto``: the layout measured fastest for the weight format - ``b200`` for bf16,
+    the reference's round robin for NVFP4 weight-only (its consumer is bound by decoding,
+    not by hand-offs, and runs one slice per instruction faster)."""
+    if requested != "auto":
+        return requested
+    return "rr" if weights == "nvfp4" else "b200"
+
+
 def make_schedule(model, schedule: str, **kwargs):
     """``b200``: the library's own layout (one SM owns all column slices of its
     down-projection rows); rr / zz / wave / dag: the reference's layout under
     that assignment policy."""
+    schedule = pick_schedule(schedule)
     from thor_megakernels_b200.demos.latency.scheduler import LatencyScheduleBuilder, build_b200_schedule
     from thor_megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
 
@@ -362,7 +385,7 @@ def run_ours(args, rank, world, local):
                 "ms_per_token": launch_ms,
                 "l2": "inputs larger than L2 (2.47 GB of weights streamed per launch vs 126 MB)",
                 "parallelism": "single",
-                "schedule": f"reference latency instruction set, layout/policy {args.schedule}, one queue per SM",
+                "schedule": f"reference latency instruction set, layout/policy {pick_schedule(args.schedule)}, one queue per SM",
             },
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": MEASURED_DRAM_TRAFFIC_PER_LAUNCH, "peak_source": peak_src,
@@ -483,7 +506,6 @@ def run_long_context(args, rank, world, local):
         cache[:, :, :ctx] = torch.randn(cache[:, :, :ctx].shape, generator=gen, device=device).bfloat16()
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     partitions = min(pick_num_attention_partitions(ctx, ntok), max(1, sms // cfg["num_key_value_heads"]))
-    sched = make_schedule(model, args.schedule, skip_attn_reduction=False, num_attention_partitions=partitions)
     peak, peak_src = measured_hbm_peak()
     kv = kv_bytes_per_position(cfg)
     kv_bytes = sum(kv * (pos + 1) + kv for pos in range(ctx, ctx + ntok)) / ntok
@@ -493,6 +515,8 @@ def run_long_context(args, rank, world, local):
     out = {}
     for fmt in ("bf16", "nvfp4"):
         quantized = nvfp4.quantize_model(model) if fmt == "nvfp4" else None
+        sched = make_schedule(model, pick_schedule(args.schedule, fmt), skip_attn_reduction=False,
+                              num_attention_partitions=partitions)
         mk = Megakernel.from_globals(sched.globs, embed_w=model.model.embed_tokens.embed_tokens.weight.data, quantized=quantized)
         sched.globs.barriers.zero_()
         for _ in range(max(args.warmup, 3)):
@@ -558,14 +582,15 @@ def measure_split_decode(workload: str, weights: str, steps: int, warmup: int, r
     fp4 = weights == "nvfp4"
     embed = model.model.embed_tokens.embed_tokens.weight.data
     if world > 1:
-        dec = TensorParallelDecoder(model, rank, world, schedule=schedule, num_attention_partitions=partitions,
-                                    nvfp4_weights=fp4)
+        dec = TensorParallelDecoder(model, rank, world, schedule=pick_schedule(schedule, weights),
+                                    num_attention_partitions=partitions, nvfp4_weights=fp4)
         mk = dec.mk
         del model  # every rank keeps only its shard (and the embedding table)
     else:
         from thor_megakernels_b200 import nvfp4
 
-        sched = make_schedule(model, schedule, skip_attn_reduction=partitions == 1, num_attention_partitions=partitions)
+        sched = make_schedule(model, pick_schedule(schedule, weights), skip_attn_reduction=partitions == 1,
+                              num_attention_partitions=partitions)
         mk = Megakernel.from_globals(sched.globs, embed_w=embed, quantized=nvfp4.quantize_model(model) if fp4 else None)
         sched.globs.barriers.zero_()
     stream = torch.cuda.current_stream(device)
@@ -642,7 +667,7 @@ def measure_split_decode(workload: str, weights: str, steps: int, warmup: int, r
             "ms_per_token": launch_ms,
             "parallelism": f"tp{world}" if world > 1 else "single",
             "attention_partitions_per_kv_head": partitions,
-            "schedule": schedule,
+            "schedule": pick_schedule(schedule, weights),
             "l2": "inputs larger than L2",
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -785,13 +810,13 @@ def build_step_model(args, device):
         gen = torch.Generator(device=device).manual_seed(3)
         for cache in model.stacked_kv_cache:
             cache[:, :, :args.pos] = torch.randn(cache[:, :, :args.pos].shape, generator=gen, device=device).bfloat16()
-        sched = make_schedule(model, args.schedule, skip_attn_reduction=args.partitions == 1,
+        sched = make_schedule(model, pick_schedule(args.schedule, args.weights), skip_attn_reduction=args.partitions == 1,
                               num_attention_partitions=args.partitions)
         sched.globs.barriers.zero_()
         return model, sched, cfg
     if args.layers is not None:
         MODEL.update(num_hidden_layers=args.layers)
-    model, sched = build_gpu_model(device, schedule=args.schedule)
+    model, sched = build_gpu_model(device, schedule=pick_schedule(args.schedule, args.weights))
     return model, sched, dict(MODEL)
 
 
@@ -1017,7 +1042,7 @@ def run_timeline(args, rank, world, local):
     if args.weights == "nvfp4":
         weights_mb *= 0.5625 / 2
     print(json.dumps({"workload": f"one step at position {args.pos}, {args.arch} shapes ({layers} layers), {args.weights} weights, "
-                                  f"schedule {args.schedule}",
+                                  f"schedule {pick_schedule(args.schedule, args.weights)}",
                       "ms_plain": plain_ms, "ms_with_stamps": stamped_ms, "layers_averaged": mid,
                       "layer_period_us": round(layer_us, 2), "layer_weight_MB": round(weights_mb, 1),
                       "times": "microseconds after the layer's first QKV instruction had its input; [earliest SM, latest SM]",
@@ -1075,9 +1100,9 @@ def main():
                     choices=["llama1b", *TP_WORKLOADS, "gemv", "llama1b-nvfp4-4k", "llama1b-batched", "batched-step", "timeline", "profile-step"],
                     help="llama1b: the headline workload (split over the GPUs when N > 1); *-tp: only the split decode")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"], help="weight format (tp, timeline, profile-step)")
-    ap.add_argument("--schedule", default="b200", choices=["b200", "rr", "zz", "wave", "dag"],
+    ap.add_argument("--schedule", default="auto", choices=["auto", "b200", "rr", "zz", "wave", "dag"],
                     help="b200: one SM owns all column slices of its down-projection rows; others: the reference's "
-                         "layout under that assignment policy")
+                         "layout under that assignment policy; auto: b200 for bf16 weights, rr for NVFP4")
     ap.add_argument("--pos", type=int, default=60, help="timeline / profile-step: position of the step")
     ap.add_argument("--layers", type=int, default=None, help="profile-step: shrink the model to this many layers")
     ap.add_argument("--arch", default="1b", choices=["1b", "8b"], help="profile-step: layer shapes")

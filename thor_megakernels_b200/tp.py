@@ -111,7 +111,7 @@ class TensorParallelDecoder:
     model can be dropped afterwards.  ``decode`` must be called by all ranks with
     the same arguments and returns the same tokens on every rank."""
 
-    def __init__(self, model, rank: int, world: int, schedule: str = "b200", group=None,
+    def __init__(self, model, rank: int, world: int, schedule: str = "auto", group=None,
                  num_attention_partitions: int = 1, nvfp4_weights: bool = False):
         import torch.distributed as dist
 
@@ -122,6 +122,8 @@ class TensorParallelDecoder:
         self.rank, self.world = rank, world
         self.local = shard_model(model, rank, world)
         split = num_attention_partitions > 1
+        if schedule == "auto":  # the layout measured fastest for the weight format
+            schedule = "rr" if nvfp4_weights else "b200"
         together = schedule == "b200"  # one SM owns all column slices of its down-projection rows
         self.schedule = LatencyScheduleBuilder.build(self.local, skip_attn_reduction=not split,
                                                      num_attention_partitions=num_attention_partitions,
