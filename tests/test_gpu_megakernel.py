@@ -166,7 +166,7 @@ def test_tiny_truncated_schedules(tiny, stop_after_op, layer_limit):
     assert torch.equal(sched.globs.barriers.cpu()[:, :6], cpu_sched.globs.barriers[:, :6])
 
 
-@pytest.mark.parametrize("partitions,context", [(2, 40), (3, 61), (8, 200), (24, 600)])
+@pytest.mark.parametrize("partitions,context", [(2, 40), (3, 61), (8, 200), (24, 600), (2, 600), (3, 2000)])
 def test_split_attention_with_reduction(partitions, context):
     """Cache split across several CTAs plus the log-sum-exp merge, against the
     oracle, with seeded N(0,1) keys/values and garbage beyond the context."""
@@ -175,8 +175,8 @@ def test_split_attention_with_reduction(partitions, context):
 
     cfg = dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
                intermediate_size=8192, vocab_size=4096)
-    cpu_model = build_model(cfg, 1024, device="cpu", seed=3)
-    model = build_model(cfg, 1024, device="cuda", seed=3)
+    cpu_model = build_model(cfg, max(1024, context + 8), device="cpu", seed=3)
+    model = build_model(cfg, max(1024, context + 8), device="cuda", seed=3)
     gen = torch.Generator().manual_seed(11)
     for idx in range(2):
         kv = torch.randn(cpu_model.stacked_kv_cache[idx].shape, generator=gen).bfloat16()

@@ -77,7 +77,7 @@ def test_llama1b_every_layer_alone_from_the_reference_residual_stream():
 # 128-wide heads, split cache + merge
 # ---------------------------------------------------------------------------
 
-@pytest.mark.parametrize("partitions,context", [(8, 1024), (24, 1500), (18, 2111)])
+@pytest.mark.parametrize("partitions,context", [(8, 1024), (24, 1500), (18, 2111), (4, 2111), (2, 1500)])
 def test_split_attention_128_wide_heads(partitions, context):
     """The attention path of the 8B shapes at long context: cache split over
     several CTAs per KV head, 128-wide heads, log-sum-exp merge; seeded N(0,1)
