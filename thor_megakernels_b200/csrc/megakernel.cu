@@ -1250,22 +1250,41 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
                     if (r < S && has_cols && try_load8(silu + ((size_t)r * width) / 2, tag, mine[r])) valid |= 1u << r;
                 }
                 named_barrier_sync(kConsumerBarrier, kConsumerThreads);  // everybody is done with the previous operand in xbuf
+                // The slices' operands are put side by side - two in xbuf, four more in the attention
+                // scratch, which no one uses during this phase - so that one barrier serves up to six
+                // slices and their tiles are taken back to back (a barrier and a trip through shared
+                // memory per slice cost more than the slice's one tile).
+                constexpr int kHalves = 6;
+                auto half_at = [&](int i) -> bf16 * {
+                    return i < 2 ? s.xbuf + i * kChunkCols : reinterpret_cast<bf16 *>(&s.attn[0][0][0]) + (i - 2) * kChunkCols;
+                };
+                static_assert(sizeof(s.attn) >= (kHalves - 2) * kChunkCols * sizeof(bf16), "attention scratch too small for four operands");
 #pragma unroll
-                for (int r = 0; r < kMaxDownSlices; ++r) {
-                    if (r >= S) break;
-                    if (ctid == 0 && r > 0) stamp(p, slot + r, kEvConsumerStart, t_start);
-                    if (has_cols && !(valid & (1u << r))) load8_wait(p, s, silu + ((size_t)r * width) / 2, tag, mine[r], op, slot + r);
-                    if (ctid == 0 && r == 0) stamp(p, slot, kEvDoneWait, t_start);
-                    bf16 *half = s.xbuf + (r & 1) * kChunkCols;
-                    *reinterpret_cast<uint4 *>(&half[ctid * 8]) = mine[r];
-                    // the half written two slices ago is free: every thread passed the barrier of the slice in between
+                for (int r0 = 0; r0 < kMaxDownSlices; r0 += kHalves) {
+                    if (r0 >= S) break;
+                    if (r0 > 0) named_barrier_sync(kConsumerBarrier, kConsumerThreads);  // the previous group's operands have been read
+#pragma unroll
+                    for (int i = 0; i < kHalves; ++i) {
+                        const int r = r0 + i;
+                        if (r >= kMaxDownSlices || r >= S) break;
+                        if (has_cols && !(valid & (1u << r))) load8_wait(p, s, silu + ((size_t)r * width) / 2, tag, mine[r], op, slot + r);
+                        if (ctid == 0 && r == 0) stamp(p, slot, kEvDoneWait, t_start);
+                        *reinterpret_cast<uint4 *>(&half_at(i)[ctid * 8]) = mine[r];
+                    }
                     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
-                    uint4 xs[1][8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) xs[0][j] = operand_convert<FP4>(lds128(&half[operand_column<FP4>(cw, t, j)]));
-                    if (ctid == 0) stamp(p, slot + r, kEvFirstUse, t_start);
-                    for (int b = b0; b < b1; ++b) consume_block<1, FP4>(p, s, st, lane, cw, xs, op, slot + r, 1, width);
-                    if (ctid == 0) stamp(p, slot + r, kEvLastUse, t_start);
+                    for (int i = 0; i < kHalves; ++i) {
+                        const int r = r0 + i;
+                        if (r >= kMaxDownSlices || r >= S) break;
+                        if (ctid == 0 && r > 0) stamp(p, slot + r, kEvConsumerStart, t_start);
+                        const bf16 *half = half_at(i);
+                        uint4 xs[1][8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) xs[0][j] = operand_convert<FP4>(lds128(&half[operand_column<FP4>(cw, t, j)]));
+                        if (ctid == 0) stamp(p, slot + r, kEvFirstUse, t_start);
+                        for (int b = b0; b < b1; ++b) consume_block<1, FP4>(p, s, st, lane, cw, xs, op, slot + r, 1, width);
+                        if (ctid == 0) stamp(p, slot + r, kEvLastUse, t_start);
+                    }
                 }
                 slot += S - 1;  // the slices' instructions have been consumed
                 next_ins = after_run;
