@@ -225,6 +225,11 @@ int mk_set_wait_budget(void *handle, int64_t cycles);
                                       * row blocks as consecutive instructions in slice order, the SM adds them to
                                       * the residual itself (same bf16 sequence as the interpreter, no cells parked
                                       * for another SM); 0: always fold across SMs */
+#define MK_OPT_COOPERATIVE_LAUNCH 5  /* 1 (default): cooperative launch, the runtime guarantees that all CTAs are
+                                      * co-resident (the reference's launch mode); 0: ordinary launch of the same
+                                      * grid - the CTAs are co-resident whenever the device runs nothing else
+                                      * (one CTA per SM, grid <= SM count); if they are not, CTAs that wait on
+                                      * one not yet scheduled do so within the wait budget */
 #define MK_OPT_MAX_INFLIGHT_TILES 2  /* weight tiles (64 KiB bf16 / 18 KiB NVFP4) one loader keeps in flight */
 #define MK_OPT_EARLY_POLL_SHIFT   1  /* consumers stop watching a dependency counter and poll the data cells
                                       * themselves once it is within target >> shift of its target; 31 = never */

@@ -27,6 +27,7 @@ MK_OPT_EARLY_POLL_SHIFT = 1
 MK_OPT_MAX_INFLIGHT_TILES = 2
 MK_OPT_DOWN_FOLD_LAST = 3
 MK_OPT_DOWN_FOLD_LOCAL = 4
+MK_OPT_COOPERATIVE_LAUNCH = 5
 
 MK_WEIGHTS_BF16 = 0
 MK_WEIGHTS_NVFP4 = 1

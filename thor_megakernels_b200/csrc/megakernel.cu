@@ -1923,6 +1923,7 @@ struct Handle {
     int fold_last_forced = 0;          // MK_OPT_DOWN_FOLD_LAST
     int fold_local_detected = 0;       // every queue keeps the slices of its row blocks together, in order
     int fold_spread_forced = 0;        // MK_OPT_DOWN_FOLD_LOCAL = 0: use the cross-SM fold even where the local one applies
+    int plain_launch = 0;              // MK_OPT_COOPERATIVE_LAUNCH = 0: ordinary launch (same grid; co-residency is then the caller's business)
     int tp_world_pending = 0;          // set by mk_tp_init, becomes params.tp_world in mk_tp_connect
     void *peer_xchg[kMaxRanks] = {};   // peers' buffers opened over CUDA IPC
 };
@@ -2254,8 +2255,11 @@ extern "C" int mk_step(void *handle, int32_t pos_id, uint32_t flags, const int32
     p.token_in = token_in;
     p.token_out = token_out;
     void *args[] = {&p};
-    cudaError_t e = cudaLaunchCooperativeKernel(kernel_for(h->nch, h->fp4), dim3(p.workers), dim3(kThreads), args,
-                                                h->smem_bytes, (cudaStream_t)stream);
+    cudaError_t e = h->plain_launch
+                        ? cudaLaunchKernel(kernel_for(h->nch, h->fp4), dim3(p.workers), dim3(kThreads), args, h->smem_bytes,
+                                           (cudaStream_t)stream)
+                        : cudaLaunchCooperativeKernel(kernel_for(h->nch, h->fp4), dim3(p.workers), dim3(kThreads), args,
+                                                      h->smem_bytes, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "cooperative megakernel launch");
     return 0;
 }
@@ -2354,6 +2358,9 @@ extern "C" int mk_set_option(void *handle, int32_t option, int64_t value) {
     case MK_OPT_DOWN_FOLD_LOCAL:
         h->fold_spread_forced = value == 0;
         h->params.down_local = h->fold_local_detected && !h->fold_last_forced && !h->fold_spread_forced;
+        return 0;
+    case MK_OPT_COOPERATIVE_LAUNCH:
+        h->plain_launch = value == 0;
         return 0;
     case MK_OPT_EARLY_POLL_SHIFT:
         if (value < 0 || value > 31) return fail(MK_ERR_BAD_ARGUMENT, "early-poll shift must be 0..31");
