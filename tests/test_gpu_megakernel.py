@@ -308,6 +308,11 @@ def test_bounded_wait_reports_status_instead_of_hanging(tiny):
     st = err.value.status
     # default: consumers poll the tagged data cells themselves -> code 5 (data never arrived)
     assert (st["code"], st["worker"], st["opcode"], st["slot"]) == (5, 0, 4, 0)
+    # per-warp record of the waits: worker 0's consumer warps were waiting for data of opcode 4, slot 0
+    stuck = mk.stuck_warps()
+    waiting = {(r["worker"], r["warp"]) for r in stuck if (r["code"], r["opcode"], r["slot"]) == (5, 4, 0)}
+    assert waiting and all(w == 0 and 1 <= warp <= 8 for w, warp in waiting)
+    assert mk.stuck_warps() == []   # reading clears the record
     # with early polling off they watch the dependency counter first -> code 1 with its value and target
     mk.set_option(MK_OPT_EARLY_POLL_SHIFT, 31)
     mk.step(0)
