@@ -1041,20 +1041,29 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, uint32_t t
     named_barrier_sync(kConsumerBarrier, kConsumerThreads);
     if (ctid == 0) stamp(p, slot, 57, t_start);  // per-warp states exchanged
 
-    // merge the 8 warps; one (head, dim) output per thread iteration
-    for (int idx = ctid; idx < kGroup * D; idx += kConsumerThreads) {
-        const int h = idx / D, d = idx % D;
-        float M = -INFINITY;
+    // merge the 8 warps; one (head, dim) output per thread and iteration.  A warp's 32 outputs belong
+    // to one head, so the eight weights exp2(m_w - M) are computed once per warp (lane w holds warp
+    // w's state) and handed round by shuffles.
+    constexpr int Dc = DPL * 8;
+    static_assert(kGroup * Dc % kConsumerThreads == 0 && Dc % 32 == 0, "a warp's outputs must share a head");
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, s.attn[w][h][kMaxHeadDim]);
-        float L = 0.f, O = 0.f;
+    for (int it = 0; it < kGroup * Dc / kConsumerThreads; ++it) {
+        const int idx = it * kConsumerThreads + ctid;
+        const int h = idx / Dc, d = idx % Dc;
+        const float mw = lane < kConsumerWarps ? s.attn[lane][h][kMaxHeadDim] : -INFINITY;
+        const float lw = lane < kConsumerWarps ? s.attn[lane][h][kMaxHeadDim + 1] : 0.f;
+        float M = mw;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) {
-            const float mw = s.attn[w][h][kMaxHeadDim];
-            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-            L = fmaf(s.attn[w][h][kMaxHeadDim + 1], f, L);
-            O = fmaf(s.attn[w][h][d], f, O);
-        }
+        for (int off = 4; off; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        M = __shfl_sync(0xffffffffu, M, 0);
+        const float fw = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        float L = fw * lw;
+#pragma unroll
+        for (int off = 4; off; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+        L = __shfl_sync(0xffffffffu, L, 0);
+        float O = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) O = fmaf(s.attn[w][h][d], __shfl_sync(0xffffffffu, fw, w), O);
         const float out = (L > 0.f) ? O / L : 0.f;
         const int head = kv_head * kGroup + h;
         // neighbouring threads hold neighbouring dimensions: the even one writes the pair's cell
