@@ -390,9 +390,12 @@ int mk_linear_batched_nvfp4(const void *w_packed, const void *w_scales_native, f
  *   sequence b reads cache rows 0..pos_ids[b]-1 of cache slot b, appends its new
  *   row at pos_ids[b] and writes its greedy token (lowest index on ties).
  *   tokens_out may be NULL.  Asynchronous on `stream`; allocates nothing, so it
- *   can be captured in a CUDA graph.
+ *   can be captured in a CUDA graph.  Token ids and positions are clamped on
+ *   the device into [0, vocab) and [0, min(kv_max_len, rope_positions)) before
+ *   anything indexes with them.
  * mk_batched_status: synchronises `stream`; MK_ERR_DEVICE_WAIT if a bounded
- *   wait inside a linear ran out.
+ *   wait inside a linear ran out, MK_ERR_BAD_ARGUMENT if a token id or position
+ *   had to be clamped since the last call.
  */
 int mk_batched_create(const MkModelDesc *desc, int32_t max_batch, void **handle);
 int mk_step_batched(void *handle, const int32_t *tokens_in, const int32_t *pos_ids, int32_t batch,

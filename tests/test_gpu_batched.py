@@ -147,6 +147,39 @@ def test_two_layer_model_independent_cache_lengths(batch):
     dec.close()
 
 
+def test_out_of_range_tokens_and_positions_are_clamped_and_reported():
+    """Token ids and positions live in device memory, so only the device can
+    check them: a value outside the vocabulary / the cache is clamped into range
+    before anything indexes with it, status() raises, and the step equals the
+    step on the clamped values."""
+    from thor_megakernels_b200._lib import MegakernelError
+    from thor_megakernels_b200.batched import BatchedDecoder
+    from thor_megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+    from thor_megakernels_b200.model_types import ExtraModelConfig
+
+    batch, max_len = 4, 64
+    model = LlamaForCausalLM.random_init(LlamaConfig(**CFG), ExtraModelConfig(interleave_rope=True, max_len_override=max_len,
+                                                                              max_batch_size=batch), seed=11, device="cuda")
+    gen = torch.Generator().manual_seed(5)
+    kv = [torch.randn(model.stacked_kv_cache[i].shape, generator=gen).bfloat16().cuda() for i in range(2)]
+    dec = BatchedDecoder(model, batch)
+
+    def run(tokens, pos):
+        for i in range(2):
+            model.stacked_kv_cache[i].copy_(kv[i])
+        out = dec.step(torch.tensor(tokens, dtype=torch.int32, device="cuda"), torch.tensor(pos, dtype=torch.int32, device="cuda")).clone()
+        return out, dec.logits.clone(), [c.clone() for c in model.stacked_kv_cache]
+
+    bad = run([5, CFG["vocab_size"] + 7, -3, 9], [10, 20, max_len + 100, -1])
+    with pytest.raises(MegakernelError):
+        dec.status()
+    good = run([5, CFG["vocab_size"] - 1, 0, 9], [10, 20, max_len - 1, 0])
+    dec.status()   # the error word was cleared, and in-range values leave it clear
+    assert torch.equal(bad[0], good[0]) and torch.equal(bad[1], good[1])
+    assert all(torch.equal(a, b) for a, b in zip(bad[2], good[2]))
+    dec.close()
+
+
 @pytest.mark.parametrize("rows,k", [(128, 256), (37, 512), (300, 2048)])
 def test_native_quantiser_is_bit_exact(rows, k):
     """Codes and scale bytes equal the numpy oracle's (oracle/nvfp4.py); the

@@ -80,11 +80,15 @@ __device__ __forceinline__ float4 lin_value4(const LinOut &o, int b, int i) {
 
 // hidden[b] = embed[token[b]]
 __global__ void embed_kernel(const bf16 *__restrict__ embed, const int *__restrict__ tokens, bf16 *__restrict__ hidden,
-                             int hidden_size) {
+                             int hidden_size, int vocab, int *__restrict__ error) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
-    const uint4 *src = reinterpret_cast<const uint4 *>(embed + (size_t)__ldg(tokens + b) * hidden_size);
+    // token ids come from device memory: one outside the table is clamped and reported (bit 1 of the error word)
+    const int t = __ldg(tokens + b);
+    const int tc = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
+    if (tc != t && threadIdx.x == 0) atomicOr(error, 2);
+    const uint4 *src = reinterpret_cast<const uint4 *>(embed + (size_t)tc * hidden_size);
     uint4 *dst = reinterpret_cast<uint4 *>(hidden + (size_t)b * hidden_size);
     for (int i = threadIdx.x; i < hidden_size / 8; i += blockDim.x) dst[i] = __ldg(src + i);
 }
@@ -515,8 +519,9 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_kernel(const bf16 *__re
 }  // namespace bo
 
 // launchers used by the batched step (batched_step.cu); declared in batched_ops.cuh
-cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int batch, int hidden_size, cudaStream_t st) {
-    return launch_pdl(bo::embed_kernel, dim3(batch), dim3(128), 0, st, embed, tokens, hidden, hidden_size);
+cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int batch, int hidden_size, int vocab, int *error,
+                         cudaStream_t st) {
+    return launch_pdl(bo::embed_kernel, dim3(batch), dim3(128), 0, st, embed, tokens, hidden, hidden_size, vocab, error);
 }
 
 cudaError_t launch_residual_norm(bf16 *hidden, const bo::LinOut &lin, int add, const bf16 *weight, bf16 *normed, int batch,
@@ -541,6 +546,22 @@ __global__ void fill_int_kernel(int *__restrict__ dst, int value, int step, int 
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = value + i * step;
+}
+
+// Positions arrive in device memory, where the host cannot look at them.  They are copied
+// into the handle's own array, clamped into [0, limit), so that no later kernel indexes
+// outside the rotary tables or the cache; a value that had to be clamped sets bit 1 of the
+// error word.
+__global__ void sanitize_positions_kernel(const int *__restrict__ pos_ids, int *__restrict__ pos_out, int batch, int pos_limit,
+                                          int *__restrict__ error) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    const int q = pos_ids[b];
+    const int qc = q < 0 ? 0 : (q >= pos_limit ? pos_limit - 1 : q);
+    pos_out[b] = qc;
+    if (qc != q) atomicOr(error, 2);
 }
 
 // Final values of the batched instruction set's dependency counters
@@ -569,6 +590,11 @@ __global__ void barrier_fill_kernel(int *__restrict__ barriers, const int *__res
 }
 
 }  // namespace bo
+
+cudaError_t launch_sanitize_positions(const int *pos_ids, int *pos_out, int batch, int pos_limit, int *error, cudaStream_t st) {
+    return launch_pdl(bo::sanitize_positions_kernel, dim3((batch + 127) / 128), dim3(128), 0, st, pos_ids, pos_out, batch, pos_limit,
+                      error);
+}
 
 cudaError_t launch_fill_int(int *dst, int value, int step, int n, cudaStream_t st) {
     return launch_pdl(bo::fill_int_kernel, dim3((n + 255) / 256), dim3(256), 0, st, dst, value, step, n);

@@ -38,12 +38,14 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int batch, int hidden_size, cudaStream_t st);
+cudaError_t launch_embed(const bf16 *embed, const int *tokens, bf16 *hidden, int batch, int hidden_size, int vocab, int *error,
+                         cudaStream_t st);
 cudaError_t launch_residual_norm(bf16 *hidden, const bo::LinOut &lin, int add, const bf16 *weight, bf16 *normed, int batch,
                                  int hidden_size, float eps, cudaStream_t st);
 cudaError_t launch_rope_append(const bo::LinOut &qkv, const int *pos_ids, const float *rope_cos, const float *rope_sin, bf16 *q_out,
                                bf16 *k_cache, bf16 *v_cache, int layer, int rows, int cache_batch, int kv_len, int hq, int hkv,
                                int hd, int half_split, int slot_fixed, cudaStream_t st);
+cudaError_t launch_sanitize_positions(const int *pos_ids, int *pos_out, int batch, int pos_limit, int *error, cudaStream_t st);
 cudaError_t launch_fill_int(int *dst, int value, int step, int n, cudaStream_t st);
 cudaError_t launch_barrier_fill(int *barriers, const int *covered, int layers, int batch, int cols, int batch_blocks, int hq,
                                 int hkv, int out_blocks, int inter_blocks, cudaStream_t st);

@@ -88,7 +88,7 @@ struct BatchedHandle {
     bool tp_bound = false, plan_ready = false;
     int covered[256] = {};        // per layer: bit (opcode - 1) set when the schedule holds that operator
     int *covered_dev = nullptr;   // device copy, for the counter fill
-    int *pos_uniform = nullptr;   // [128] the step's position, one per sequence of a block
+    int *pos_uniform = nullptr;   // [128] positions of the rows of a pass (clamped copies of the caller's, or generated)
 };
 
 int fail_msg(int code, const char *text) {
@@ -377,10 +377,12 @@ extern "C" int mk_step_batched(void *handle, const int32_t *tokens_in, const int
     const MkModelDesc &d = h->d;
     if (batch > d.kv_batch) return fail_msg(MK_ERR_BAD_ARGUMENT, "mk_step_batched: the cache holds fewer sequences than the batch");
     Runner r;
-    r.h = h; r.st = (cudaStream_t)stream; r.pos_ids = pos_ids; r.rows = batch; r.half_split = 0; r.slice_down = 1;
+    // the kernels index with clamped copies of the caller's positions (bit 1 of the error word if any was out of range)
+    r.h = h; r.st = (cudaStream_t)stream; r.pos_ids = h->pos_uniform; r.rows = batch; r.half_split = 0; r.slice_down = 1;
     r.b = StepBuffers{(bf16 *)d.hidden_states, (bf16 *)d.logits, h->normed, h->normed, h->normed, h->q, h->attn, h->act,
                       (bf16 *)d.k_cache, (bf16 *)d.v_cache};
-    r.ok(launch_embed((const bf16 *)d.embed_w, tokens_in, r.b.hidden, batch, d.hidden_size, r.st));
+    r.ok(launch_sanitize_positions(pos_ids, h->pos_uniform, batch, std::min(d.kv_max_len, d.rope_positions), h->error_word, r.st));
+    r.ok(launch_embed((const bf16 *)d.embed_w, tokens_in, r.b.hidden, batch, d.hidden_size, d.vocab_size, h->error_word, r.st));
     for (int l = 0; l < d.num_layers && r.code == 0; ++l) {
         r.attn_norm(l); r.qkv(l); r.attention(l); r.o_proj(l); r.mlp_norm(l); r.gate_up(l, true); r.down_proj(l);
     }
@@ -412,7 +414,7 @@ extern "C" int mk_prefill_batched(void *handle, const int32_t *tokens, int32_t c
         r.h = h; r.st = st; r.pos_ids = h->pos_uniform; r.rows = rows; r.half_split = 0; r.slice_down = 1; r.slot_fixed = slot;
         r.b = StepBuffers{(bf16 *)d.hidden_states, (bf16 *)d.logits, h->normed, h->normed, h->normed, h->q, h->attn, h->act,
                           (bf16 *)d.k_cache, (bf16 *)d.v_cache};
-        r.ok(launch_embed((const bf16 *)d.embed_w, tokens + c0, r.b.hidden, rows, d.hidden_size, st));
+        r.ok(launch_embed((const bf16 *)d.embed_w, tokens + c0, r.b.hidden, rows, d.hidden_size, d.vocab_size, h->error_word, st));
         for (int l = 0; l < d.num_layers && r.code == 0; ++l) {
             r.attn_norm(l); r.qkv(l); r.attention(l); r.o_proj(l); r.mlp_norm(l); r.gate_up(l, true); r.down_proj(l);
         }
@@ -585,7 +587,8 @@ extern "C" int mk_batched_status(void *handle, void *stream) {
     if (e != cudaSuccess) return fail_msg((int)e, cudaGetErrorString(e));
     if (word != 0) {
         cudaMemset(h->error_word, 0, sizeof(int));
-        return fail_msg(MK_ERR_DEVICE_WAIT, "a bounded wait inside a batched linear ran out");
+        if (word & 1) return fail_msg(MK_ERR_DEVICE_WAIT, "a bounded wait inside a batched linear ran out");
+        return fail_msg(MK_ERR_BAD_ARGUMENT, "a token id or position given to a batched step or prefill was outside the vocabulary / the cache and rotary tables; it was clamped");
     }
     return 0;
 }

@@ -83,7 +83,7 @@ constexpr int kLocalBlocks = 8;   // row blocks of one down-projection instructi
 
 // timing slots (reference include/util.cuh:225-256)
 constexpr int kEvLoaderStart = 5, kEvStorerStart = 9, kEvConsumerStart = 11;
-constexpr int kEvAtWait = 44, kEvDoneWait = 45, kEvFirstLoad = 48, kEvFirstUse = 49, kEvFirstStore = 50;
+constexpr int kEvAtWait = 44, kEvDoneWait = 45, kEvFirstUse = 49, kEvFirstStore = 50;
 constexpr int kEvLastLoad = 51, kEvLastUse = 52, kEvLastStore = 53, kEvOutputReady = 54;
 
 // status codes
@@ -887,7 +887,6 @@ __device__ void attention_partial(const Params &p, Smem &s, int ctid, uint32_t t
     const int lane = ctid & 31, cw = ctid >> 5;
     const int layer = __ldg(ins + 1), kv_head = __ldg(ins + 2), num_partials = __ldg(ins + 3), part = __ldg(ins + 4);
     const int D = p.hd;
-    const int blocks_per_head = D / kBlockRows;
 
     const int seq_len = p.pos + 1;
     const int total_blocks = (seq_len + 15) / 16;
@@ -1169,6 +1168,15 @@ __device__ void attention_reduction(const Params &p, Smem &s, int ctid, uint32_t
     }
 }
 
+// The token id is read from device memory, where the host cannot check it: one outside the
+// table (whole vocabulary = this rank's rows x ranks) is clamped to its nearest row.
+__device__ __forceinline__ const bf16 *embedding_row(const Params &p) {
+    const int rows = p.vocab * p.tp_world;
+    int t = __ldg(p.token_in);
+    t = t < 0 ? 0 : (t >= rows ? rows - 1 : t);
+    return p.embed_w + (size_t)t * p.hidden;
+}
+
 template <int NCH, bool FP4>
 __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_start) {
     const int lane = ctid & 31, cw = ctid >> 5;
@@ -1176,7 +1184,7 @@ __device__ void consumer_role(const Params &p, Smem &s, int ctid, long long t_st
     const uint32_t tag = __ldg(p.epoch);
     // layer-0 input: the embedding row of the fed-back token, or the host-written hidden state
     const bf16 *step_input = p.hidden_states;
-    if (p.flags & MK_STEP_EMBED) step_input = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
+    if (p.flags & MK_STEP_EMBED) step_input = embedding_row(p);
 
     InsWords next_ins = fetch_instruction(p, 0, lane);
 #pragma unroll 1
@@ -1535,7 +1543,7 @@ __device__ void storer_role(const Params &p, Smem &s, int lane, long long t_star
     const int k_start = p.hq * D, v_start = k_start + p.hkv * D;
     const uint32_t tag = __ldg(p.epoch);
     const bf16 *step_input = p.hidden_states;
-    if (p.flags & MK_STEP_EMBED) step_input = p.embed_w + (size_t)__ldg(p.token_in) * p.hidden;
+    if (p.flags & MK_STEP_EMBED) step_input = embedding_row(p);
     const bool writer = lane < kBlockRows;              // lanes that own an output row
     const bool pair_writer = writer && (lane & 1) == 0;  // ... and write the cell of rows (lane, lane+1)
     int run_start = -1, run_layer = -1;                 // consecutive down-projection instructions of one layer
