@@ -55,6 +55,8 @@ import torch  # noqa: E402
 
 PROMPT_LEN = 16
 TOKENS_PER_REQUEST = 100
+# the headline request; both arms (this library and --impl reference) and every N name it the same way
+HEADLINE_WORKLOAD = "llama-3.2-1b-arch bf16 batch-1 greedy decode: 16-token context, 100 tokens (pos 16..115)"
 FALLBACK_HBM_GBS = 6650.0  # used only when MEASURED_PEAKS.json is absent
 
 MODEL = dict(hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
@@ -293,8 +295,8 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(times),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "llama-3.2-1b-arch bf16 batch-1 greedy decode, 16-token context, positions 16..",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": HEADLINE_WORKLOAD,
                    "step": "one decode token on the host cores (bounded sample of the 100-token request)"},
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": f"{len(times)} decode tokens of the 16-layer model, PyTorch interpreter, {threads} threads"},
@@ -380,7 +382,7 @@ def run_ours(args, rank, world, local):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {
                 "workload": ("SELF-TEST (2 layers, small vocabulary) - not the benchmark workload" if args.self_test else
-                             "llama-3.2-1b-arch bf16 batch-1 greedy decode: 16-token context, 100 tokens (pos 16..115)"),
+                             HEADLINE_WORKLOAD),
                 "step": "one 100-token request = 100 megakernel launches",
                 "ms_per_token": launch_ms,
                 "l2": "inputs larger than L2 (2.47 GB of weights streamed per launch vs 126 MB)",
@@ -788,8 +790,8 @@ def run_headline_split(args, rank, world, local):
     torch.cuda.empty_cache()
     big = None if args.no_8b else llama8b_records(args, rank, world, local)
     if rank == 0:
-        line["config"]["workload"] = ("llama-3.2-1b-arch bf16 batch-1 greedy decode: 16-token context, 100 tokens (pos 16..115), "
-                                      f"model split over {world} GPUs")
+        if not args.self_test:
+            line["config"]["workload"] = HEADLINE_WORKLOAD   # the same request at every N; config.parallelism says how it is split
         line["tp_parity"] = parity
         line["llama8b_tp"] = big
         print(json.dumps(line), flush=True)
